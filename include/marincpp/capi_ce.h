@@ -1,0 +1,82 @@
+/* Further C entry points of the fused CE in libmarincpp_kernels.so. The first block has the names and signatures of
+ * the reference's src/kernels/cross_entropy/capi_ce.h:17-35 (test and bench entry points); the second block holds the
+ * extensions of this library: z-loss / ignore-index, and the data-parallel dW reduction. Conventions as in capi.h. */
+#ifndef MARINCPP_CAPI_CE_H
+#define MARINCPP_CAPI_CE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* reference capi_ce.h:17-19. This library has one kernel set, so the arguments only update the recorded setting;
+ * returns the previous setting packed as dgrad | wgrad << 1 | sm90 << 2 (sm90 < 0: unchanged). */
+int nm_ce_set_backends(int dgrad_own, int wgrad_own, int sm90);
+/* reference capi_ce.h:20-21. The statistics exponential here is always ex2.approx on a pre-scaled argument; the
+ * switch is recorded and returned for callers that toggle it. */
+int nm_ce_set_fast_stats_exp(int on);
+/* reference capi_ce.h:22-23: dw += f32(bf16(dw_microbatch)); dw_microbatch = 0 (n = V * D) */
+int nm_ce_finish_microbatch(float* dw, float* dw_microbatch, int64_t n, void* stream);
+/* reference capi_ce.h:24-25: *out = mult / sum(w[0..n)) in f32, fixed summation order */
+int nm_ce_grad_scale(const float* w, int64_t n, float mult, float* out, void* stream);
+/* reference capi_ce.h:26-31: one readout head (norm of `state`, CE against w, dW into dw, d(state) added into d_state,
+ * gain partials [nm_norm_partial_rows(T), D] into dgain_partial) */
+int nm_ce_readout(int impl, int rounding, int logits_store, const void* state, const void* norm_gain,
+                  float* norm_rstd_ws, void* norm_out_ws, const void* w, float* dw, float* dgain_partial,
+                  const float* grad_scale, void* d_state, int visible_dims, const int32_t* targets,
+                  const float* weight, float* loss_tok, float* lse, float* loss_partial, int forward_only, int64_t T,
+                  int D, int V, int chunk_rows, float eps, void* workspace, void* stream);
+/* reference capi_ce.h:32-34: the in-place dlogits pass alone over a logits store [rows, ldS]. `gscale` holds the
+ * per-row factor g; the store is rewritten as bf16 g (p - onehot). logits_store 0 f32, 1 bf16. */
+int nm_ce_dlogits(int logits_store, void* store, int64_t ldS, const float* lse, const float* gscale,
+                  const int32_t* targets, int rows, int V, void* stream);
+/* reference capi_ce.h:35: compute capability as the CE dispatch sees it (100 on a B200) */
+int nm_ce_device_arch(void);
+
+/* ---------------------------------------------------------------------------------------------- extensions
+ * (no counterpart in the reference, whose CE has neither a z-loss nor an ignore index: docs/spec/model.md:277) */
+
+/* nm_fused_linear_ce plus: z_loss_weight L (loss += L lse^2, dz = g (p (1 + 2 L lse) - onehot)), ignore_index (a
+ * target equal to it is ignored like a target outside [0, V)), and dw_reducer (NULL, or a handle from
+ * nm_grad_reducer_create: the dW kernel of the last chunk is issued per vocabulary bucket and each bucket's all-reduce
+ * is enqueued on the reducer's stream as soon as that bucket is final, overlapping the last chunk's dX kernel). */
+int nm_fused_linear_ce_ex(int impl, int rounding, int io, int logits_store, const void* x, const void* w,
+                          const int32_t* targets, const float* weight, const float* grad_scale,
+                          const float* logit_bias, float* loss_tok, float* lse, float* loss_partial, void* dx,
+                          int accumulate_dx, float* dw, float* dw_microbatch, int dw_round, int forward_only,
+                          int64_t T, int D, int V, int chunk_rows, void* workspace, void* stream,
+                          float z_loss_weight, int32_t ignore_index, void* dw_reducer);
+
+/* Status word of the device-side waits: every mbarrier wait in the tcgen05 kernels is bounded; a wait that runs out
+ * sets a bit in a per-workspace word and the kernel returns. Reads the word of `workspace` (synchronises `stream`). */
+int nm_ce_device_status(void* workspace, void* stream, uint32_t* status_host);
+
+/* One of the three tcgen05 contractions alone, for unit tests and ncu (kind 0: C[M,N] f32 = A[M,K] B[N,K]^T, both
+ * K-major; 1: C[M,N] f32 = A[M,K] B[K,N], B N-major; 2: C[M,N] f32 = A[K,M]^T B[K,N], both MN-major). bf16 operands,
+ * row-major with leading dimensions in elements; `status` is a device uint32 the kernel ORs its wait errors into. */
+int nm_ce_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,
+                    int N, int K, uint32_t* status, void* stream);
+
+/* ---- data-parallel dW reduction over NCCL (the role of the reference's include/marincpp/comm.hpp:22-58 GradReducer
+ *      and of src/train/trainer.cpp:50,139): one communicator per process (one process per GPU) ------------------- */
+int nm_comm_unique_id(void* id128_host);                       /* rank 0: 128 bytes to broadcast to the other ranks */
+int nm_comm_create(const void* id128_host, int nranks, int rank, void** comm_out);   /* current device */
+int nm_comm_destroy(void* comm);
+int nm_comm_allreduce_f32(void* comm, float* buf, int64_t n, void* stream);           /* in place, sum */
+/* A reducer over one gradient buffer grad[V, D] f32 split into n_buckets contiguous vocabulary ranges (multiples of
+ * 128 rows). reduce_dtype 0: f32 in place; 1: each bucket is cast to bf16 into `staging` (V * D * 2 bytes, caller
+ * owned), all-reduced in bf16 and cast back. */
+int nm_grad_reducer_create(void* comm, float* grad, int V, int D, int n_buckets, int reduce_dtype, void* staging,
+                           void** reducer_out);
+int nm_grad_reducer_destroy(void* reducer);
+/* all buckets, in order, after the work already on `stream` (no overlap: what trainer.cpp:139 does) */
+int nm_grad_reducer_reduce_all(void* reducer, void* stream);
+/* make `stream` wait for every bucket reduction enqueued so far */
+int nm_grad_reducer_wait(void* reducer, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif
