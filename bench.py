@@ -1,0 +1,420 @@
+"""Benchmark of the fused LM-head cross-entropy (forward + dX + dW) through the C ABI of libmarincpp_kernels.so.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c1|c2|c3|c4] [--impl ours|reference]
+
+One "step" is one fused-CE forward + backward over one batch of synthetic input of the named configuration (per GPU:
+131072 tokens; c3 = hidden 2048 x vocab 128256, Zipf(1.1) labels, 1% ignored, z-loss 1e-4), plus, on N > 1 GPUs, the
+bucketed NCCL all-reduce of dW overlapped with the last chunk's dX kernel. Rows are sharded by rank (weak scaling);
+W is replicated. Rank 0 prints ONE JSON line:
+  value      tokens/s of the whole job with inputs resident in HBM (CUDA events on the launching stream, max over ranks)
+  e2e        the same through the same C-ABI call with HOST inputs: each step copies x, targets and weights from pinned
+             host memory (double-buffered on a copy stream) and reads the per-chunk losses back
+  roofline   the slowest of the three tcgen05 kernels: 2 T D V FLOP per step / its event-timed seconds per step,
+             against the measured dense bf16 peak (MEASURED_PEAKS.json, sustained figure: the kernel is timed inside a
+             long step); path_* are the same for the whole 6 T D V path
+  cpu_baseline  the CPU oracle (oracle/ce_ref.c, OpenMP on all host cores) timed on a bounded row sample (N = 1 only)
+--impl reference times the reference's CPU-side computation of this path: the reference has no CPU implementation
+(its f32 "reference" is a GPU path), so the arm runs the CPU oracle port on the host cores, a bounded row sample per step.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "marin.cpp_b200"))
+
+CONFIGS = {
+    # name: (D, V, tokens per GPU, labels, ignore fraction, z-loss, dW reduce dtype, readouts)
+    "c1": dict(D=512, V=128256, T=131072, labels="uniform", ignore=0.02, z_loss=1e-4, reduce="f32", readouts=1),
+    "c2": dict(D=1024, V=128256, T=131072, labels="uniform", ignore=0.02, z_loss=0.0, reduce="bf16", readouts=1),
+    "c3": dict(D=2048, V=128256, T=131072, labels="zipf", ignore=0.01, z_loss=1e-4, reduce="f32", readouts=1),
+    "c4": dict(D=512, V=128256, T=16384, labels="uniform", ignore=0.02, z_loss=0.0, reduce="f32", readouts=48),
+}
+WORKLOAD = {
+    "c1": "fused CE fwd+bwd, 131072 tok/GPU x hidden 512 x vocab 128256 (Qwen3-130m head), bf16, uniform labels 2% ignored, z-loss 1e-4",
+    "c2": "fused CE fwd+bwd, 131072 tok/GPU x hidden 1024 x vocab 128256 (Qwen3-520m head), bf16, uniform labels 2% ignored, bf16 dW all-reduce",
+    "c3": "fused CE fwd+bwd, 131072 tok/GPU x hidden 2048 x vocab 128256 (Qwen3-1.2B head), bf16, Zipf(1.1) labels 1% ignored, z-loss 1e-4",
+    "c4": "48 readouts x 16384 tok/GPU x hidden 512 x vocab 128256 (pls shared head), bf16, one dW all-reduce per step",
+}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(burst=float(d["bf16_tflops"]), sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    hbm=float(d["hbm_gbs"]), source="measured")
+    return dict(burst=1590.0, sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs (read-only queries)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_inputs(torch, cfg, rank, device, layer=0):
+    """Seeded synthetic inputs of the configuration on the device: x rows ~ N(0,1) RMS-normalised, W ~ N(0, 0.02^2),
+    bf16; labels uniform or Zipf(1.1) with a fraction set to -100; weight = 1[label != -100]. W and the labels do not
+    depend on `layer`; x does (independent readout states)."""
+    T, D, V = cfg["T"], cfg["D"], cfg["V"]
+    gw = torch.Generator(device=device).manual_seed(0xC0DE)
+    W = (torch.randn(V, D, generator=gw, device=device) * 0.02).to(torch.bfloat16)
+    gx = torch.Generator(device=device).manual_seed(1000 + 97 * rank + layer)
+    X = torch.randn(T, D, generator=gx, device=device)
+    X = (X / X.pow(2).mean(dim=1, keepdim=True).sqrt()).to(torch.bfloat16)
+    gy = torch.Generator(device=device).manual_seed(5000 + rank)
+    if cfg["labels"] == "zipf":
+        # inverse-CDF Zipf(1.1) over ranks 1..V from seeded uniforms; rank 1 is id 0
+        pk = 1.0 / torch.arange(1, V + 1, dtype=torch.float64, device=device) ** 1.1
+        cdf = torch.cumsum(pk, 0)
+        cdf = cdf / cdf[-1]
+        u = torch.rand(T, generator=gy, device=device, dtype=torch.float64)
+        Y = torch.searchsorted(cdf, u, right=True).clamp_(max=V - 1).to(torch.int32)
+    else:
+        Y = torch.randint(0, V, (T,), generator=gy, device=device, dtype=torch.int32)
+    Y[torch.rand(T, generator=gy, device=device) < cfg["ignore"]] = -100
+    WT = (Y != -100).float()
+    return X, W, Y, WT
+
+
+def cpu_sample(cfg, seconds=12.0, rows0=32):
+    """Times the CPU oracle on the first rows of rank 0's batch; returns (tokens/s, rows, threads, seconds)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ce_oracle as O
+    c = O.COracle()
+    D, V = cfg["D"], cfg["V"]
+    x, w, y, wt = O.make_inputs(1024, D, V, seed=0xC3, ignore_frac=cfg["ignore"], labels=cfg["labels"])
+    dw = None
+
+    def run(n):
+        nonlocal dw
+        t = time.perf_counter()
+        _, _, _, dw = c.run(x[:n], w, y[:n], wt[:n], 1.0 / max(1.0, float(wt[:n].sum())), z_loss=cfg["z_loss"],
+                            ignore_index=-100, dw_out=dw)
+        return time.perf_counter() - t
+    t0 = run(rows0)
+    n = int(max(rows0, min(1024, rows0 * seconds / max(t0, 1e-3))))
+    n -= n % 4
+    t1 = run(n)
+    return n / t1, n, c.threads(), t1
+
+
+def reference_arm(args, cfg, rank, world):
+    """The reference arm: the reference has no CPU implementation of this path, so this times the CPU oracle port
+    (oracle/ce_ref.c) on the host cores; each step is a bounded row sample of the configuration."""
+    if rank != 0:
+        return
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ce_oracle as O
+    c = O.COracle()
+    D, V = cfg["D"], cfg["V"]
+    rows = 64
+    x, w, y, wt = O.make_inputs(rows, D, V, seed=0xC3, ignore_frac=cfg["ignore"], labels=cfg["labels"])
+    gs = 1.0 / max(1.0, float(wt.sum()))
+    dw = None
+    for _ in range(args.warmup):
+        _, _, _, dw = c.run(x, w, y, wt, gs, z_loss=cfg["z_loss"], ignore_index=-100, dw_out=dw)
+    t = time.perf_counter()
+    for _ in range(args.steps):
+        _, _, _, dw = c.run(x, w, y, wt, gs, z_loss=cfg["z_loss"], ignore_index=-100, dw_out=dw)
+    dt = time.perf_counter() - t
+    val = rows * args.steps / dt
+    sample = f"{rows} rows of the {args.config} batch per step (cost is linear in rows), full vocabulary"
+    print(json.dumps({
+        "impl": "reference", "metric": "fused_ce_fwd_bwd_tokens_per_s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD[args.config], "note": "CPU oracle port on the host cores; the reference ships "
+                   "no CPU implementation of this path"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": c.threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--chunk", type=int, default=16384)
+    ap.add_argument("--buckets", type=int, default=8)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.warmup < 3:
+        args.warmup = 3 if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        reference_arm(args, cfg, rank, world)
+        return
+
+    import torch
+    import nmce
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    lib = nmce.Lib()
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    T, D, V, L = cfg["T"], cfg["D"], cfg["V"], cfg["z_loss"]
+    R = cfg["readouts"]
+    chunk = min(args.chunk, T)
+    n_chunks = (T + chunk - 1) // chunk
+
+    X, W, Y, WT = make_inputs(torch, cfg, rank, dev)
+    Xs = [X] + [make_inputs(torch, cfg, rank, dev, layer=l)[0] for l in range(1, R)]
+    wsum = WT.sum().double().reshape(1)
+    if dist:
+        dist.all_reduce(wsum)
+    gs = (1.0 / wsum).float().to(dev)                      # global mean over non-ignored tokens (and readouts below)
+    if R > 1:
+        gs = gs / R
+    dx = torch.empty_like(X)
+    dw = torch.zeros(V, D, dtype=torch.float32, device=dev)
+    loss = torch.empty(T, dtype=torch.float32, device=dev)
+    lse = torch.empty(T, dtype=torch.float32, device=dev)
+    lp = torch.zeros(R, n_chunks, dtype=torch.float32, device=dev)
+    ws = torch.empty(lib.nm_ce_workspace_bytes(1, T, D, V, chunk, 1), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev)
+    sp = ctypes.c_void_p(stream.cuda_stream)
+
+    comm = reducer = staging = None
+    if world > 1:
+        idbuf = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            lib.nm_comm_unique_id(nmce.ptr(idbuf))
+        idg = idbuf.to(dev)
+        dist.broadcast(idg, 0)
+        idbuf = idg.cpu()
+        comm = ctypes.c_void_p()
+        lib.nm_comm_create(nmce.ptr(idbuf), world, rank, ctypes.byref(comm))
+        if cfg["reduce"] == "bf16":
+            staging = torch.empty(V, D, dtype=torch.bfloat16, device=dev)
+        reducer = ctypes.c_void_p()
+        lib.nm_grad_reducer_create(comm, nmce.ptr(dw), V, D, args.buckets, 1 if cfg["reduce"] == "bf16" else 0,
+                                   nmce.ptr(staging), ctypes.byref(reducer))
+
+    def ce(x_in, y_in, wt_in, r, last):
+        lib.nm_fused_linear_ce_ex(1, 0, 1, 1, nmce.ptr(x_in), nmce.ptr(W), nmce.ptr(y_in), nmce.ptr(wt_in),
+                                  nmce.ptr(gs), None, nmce.ptr(loss), nmce.ptr(lse), nmce.ptr(lp[r]), nmce.ptr(dx), 0,
+                                  nmce.ptr(dw), None, 0, 0, T, D, V, chunk, nmce.ptr(ws), sp, float(L), -100,
+                                  reducer if last else None)
+
+    def step(inputs=None):
+        """zero dW, every readout's fused CE (dW accumulates), the dW all-reduce overlapped with the last dX."""
+        dw.zero_()
+        for r in range(R):
+            x_in, y_in, wt_in = inputs if inputs is not None else (Xs[r], Y, WT)
+            ce(x_in, y_in, wt_in, r, last=(r == R - 1))
+        if reducer:
+            lib.nm_grad_reducer_wait(reducer, sp)
+
+    def barrier():
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def check_status():
+        st = ctypes.c_uint32(0)
+        lib.nm_ce_device_status(nmce.ptr(ws), sp, ctypes.byref(st))
+
+    launches_per_step = R * (n_chunks * 6)                 # logits, finalize, dlogits, dW, dX, chunk loss per chunk
+    if reducer:                                            # the last chunk's dW runs per bucket (+ the bf16 casts)
+        launches_per_step += (args.buckets - 1) + (2 * args.buckets if cfg["reduce"] == "bf16" else 0)
+
+    # ---------------------------------------------------------------- device-resident timing (value)
+    for _ in range(args.warmup):
+        step()
+    check_status()
+    lib.nm_ce_profile_enable(launches_per_step * args.steps + 64)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop()
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if dist:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+    prof_ms = (ctypes.c_double * 6)()
+    prof_n = (ctypes.c_int * 6)()
+    lib.nm_ce_profile_read(prof_ms, prof_n)
+    lib.nm_ce_profile_enable(0)
+    check_status()
+    loss_value = float((lp.double().sum() * gs.double()).item())
+
+    # ---------------------------------------------------------------- host-input timing (e2e)
+    e2e = None
+    if not args.no_e2e:
+        hx = [torch.empty(T, D, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        hy = [torch.empty(T, dtype=torch.int32).pin_memory() for _ in range(2)]
+        hw = [torch.empty(T, dtype=torch.float32).pin_memory() for _ in range(2)]
+        for b in range(2):
+            hx[b].copy_(X)
+            hy[b].copy_(Y)
+            hw[b].copy_(WT)
+        dxin = [torch.empty_like(X) for _ in range(2)]
+        dyin = [torch.empty_like(Y) for _ in range(2)]
+        dwin = [torch.empty_like(WT) for _ in range(2)]
+        hlp = torch.empty(R, n_chunks, dtype=torch.float32).pin_memory()
+        copy_stream = torch.cuda.Stream(dev)
+        ready = [torch.cuda.Event() for _ in range(2)]
+        freed = [torch.cuda.Event() for _ in range(2)]
+
+        def upload(b):
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(freed[b])
+                dxin[b].copy_(hx[b], non_blocking=True)
+                dyin[b].copy_(hy[b], non_blocking=True)
+                dwin[b].copy_(hw[b], non_blocking=True)
+                ready[b].record(copy_stream)
+
+        def e2e_steps(k):
+            for b in range(2):
+                freed[b].record(stream)
+            upload(0)
+            for i in range(k):
+                b = i & 1
+                if i + 1 < k:
+                    upload(b ^ 1)                       # next step's inputs travel while this step computes
+                stream.wait_event(ready[b])
+                step((dxin[b], dyin[b], dwin[b]))
+                freed[b].record(stream)
+                hlp.copy_(lp, non_blocking=True)        # the step's result: per-chunk weighted losses
+            stream.synchronize()
+
+        e2e_steps(args.warmup)
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record(stream)
+        e2e_steps(args.steps)
+        f1.record(stream)
+        barrier()
+        ms2 = torch.tensor([f0.elapsed_time(f1)], dtype=torch.float64, device=dev)
+        if dist:
+            dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
+        check_status()
+        h2d = T * D * 2 + T * 4 + T * 4                  # one upload of x, targets, weights per step
+        e2e = {"value": world * R * T * args.steps / (float(ms2.item()) * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": R * n_chunks * 4,
+               "ms_per_step": float(ms2.item()) / args.steps}
+
+    # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        v, n, threads, secs = cpu_sample(cfg)
+        cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": f"first {n} rows of the batch, full vocabulary, {secs:.1f} s (cost is linear in rows)"}
+
+    if reducer:
+        lib.nm_grad_reducer_destroy(reducer)
+        lib.nm_comm_destroy(comm)
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    pk = peaks()
+    tokens = world * R * T * args.steps
+    ms_step = ms_total / args.steps
+    flop_step = 6.0 * R * T * D * V                                  # per GPU
+    path_tflops = flop_step / (ms_step * 1e-3) / 1e12
+    names = ["logits", "finalize", "dlogits", "dw", "dx", "chunk_loss"]
+    per_class = {names[i]: {"ms_per_step": prof_ms[i] / args.steps, "launches_per_step": prof_n[i] / args.steps}
+                 for i in range(6)}
+    gemm = {k: per_class[k]["ms_per_step"] for k in ("logits", "dw", "dx")}
+    dom = max(gemm, key=gemm.get)
+    dom_launch_ms = prof_ms[names.index(dom)] / max(1, prof_n[names.index(dom)])
+    dom_flop_launch = 2.0 * R * T * D * V * args.steps / max(1, prof_n[names.index(dom)])
+    achieved = dom_flop_launch / (dom_launch_ms * 1e-3) / 1e12
+    out = {
+        "metric": "fused_ce_fwd_bwd_tokens_per_s", "value": tokens / (ms_total * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD[args.config], "tokens_per_gpu": R * T, "hidden": D, "vocab": V,
+                   "chunk_rows": chunk, "readouts": R, "parallelism": f"dp{world} (rows sharded, W replicated)",
+                   "dw_allreduce": (f"{cfg['reduce']}, {args.buckets} buckets, overlapped with the last dX" if world > 1
+                                    else "none (1 GPU)"),
+                   "l2": "inputs (x, W, logits store: > 5 GB per step) exceed the 126 MB L2; no flush needed",
+                   "loss": loss_value},
+        "clocks": clocks,
+        "e2e": e2e,
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "tensor", "kernel": f"k_ce_umma<{dom}>", "achieved": achieved, "peak": pk["sustained"],
+                     "unit": "TFLOP/s", "frac": achieved / pk["sustained"], "traffic": None,
+                     "peak_source": f"{pk['source']} (sustained; burst {pk['burst']})",
+                     "frac_of_burst": achieved / pk["burst"], "launch_ms": dom_launch_ms,
+                     "path_tflops": path_tflops, "path_frac": path_tflops / pk["sustained"],
+                     "path_frac_of_burst": path_tflops / pk["burst"], "per_kernel_class": per_class},
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -52,6 +52,14 @@ int nm_fused_linear_ce_ex(int impl, int rounding, int io, int logits_store, cons
  * sets a bit in a per-workspace word and the kernel returns. Reads the word of `workspace` (synchronises `stream`). */
 int nm_ce_device_status(void* workspace, void* stream, uint32_t* status_host);
 
+/* Per-kernel-class device timing for benches (the role of the reference's tests/s5/bench_ce.py event timing, moved
+ * inside the call so that each kernel class is timed on the stream it is launched on). enable(n > 0) creates 2 n CUDA
+ * events and makes every later call bracket each launch with a pair (up to n launches between two reads);
+ * enable(0) frees them. read() waits for the recorded events and returns, per class (0 logits, 1 finalize, 2 dlogits
+ * pass, 3 dW, 4 dX, 5 chunk loss), the summed milliseconds and the number of launches since the previous read. */
+int nm_ce_profile_enable(int max_launches);
+int nm_ce_profile_read(double* ms_host /*[6]*/, int* launches_host /*[6]*/);
+
 /* One of the three tcgen05 contractions alone, for unit tests and ncu (kind 0: C[M,N] f32 = A[M,K] B[N,K]^T, both
  * K-major; 1: C[M,N] f32 = A[M,K] B[K,N], B N-major; 2: C[M,N] f32 = A[K,M]^T B[K,N], both MN-major). bf16 operands,
  * row-major with leading dimensions in elements; `status` is a device uint32 the kernel ORs its wait errors into. */

@@ -1,0 +1,62 @@
+// Data-parallel reduction of the LM-head gradient over NCCL: the part of the reference's communication design that
+// the fused CE path touches. The reference declares a bucketed GradReducer (include/marincpp/comm.hpp:22-58) but ships
+// no implementation; its trainer all-reduces the whole f32 gradient once per step on the compute stream
+// (src/train/trainer.cpp:50,139). Here: one communicator per process (one process per GPU), a dedicated communication
+// stream, and a reducer over dW [V, D] split into vocabulary-range buckets. The fused CE issues the dW kernel of its
+// last chunk bucket by bucket and calls bucket_ready() after each, so the all-reduce of bucket i runs on the
+// communication stream while the dW kernel of bucket i + 1 and then the dX kernel run on the compute stream.
+#pragma once
+
+#include <cstdint>
+#include <vector>
+
+#include "marincpp/core.hpp"
+
+typedef struct CUevent_st* cudaEvent_t;
+
+namespace nm {
+
+class Comm {
+ public:
+  static void unique_id(void* id128_host);                     // rank 0; 128 bytes
+  Comm(const void* id128_host, int nranks, int rank);          // binds the current device
+  ~Comm();
+  Comm(const Comm&) = delete;
+  Comm& operator=(const Comm&) = delete;
+  int nranks() const { return nranks_; }
+  int rank() const { return rank_; }
+  cudaStream_t stream() const { return stream_; }              // the communication stream
+  void allreduce_sum(void* buf, int64_t n, DType dt, cudaStream_t st);   // in place; dt f32 or bf16
+ private:
+  void* comm_ = nullptr;
+  cudaStream_t stream_ = nullptr;
+  int nranks_ = 1, rank_ = 0, device_ = 0;
+};
+
+class GradReducer {
+ public:
+  // grad [V, D] f32; n_buckets contiguous vocabulary ranges whose sizes are multiples of 128 rows (the last takes the
+  // remainder). reduce_dtype f32: in place. bf16: each bucket is cast into `staging` (V * D bf16, caller owned),
+  // all-reduced there and cast back (wire bytes halved; the sum is then a bf16 sum).
+  GradReducer(Comm& comm, float* grad, int V, int D, int n_buckets, DType reduce_dtype, void* staging);
+  ~GradReducer();
+  GradReducer(const GradReducer&) = delete;
+  GradReducer& operator=(const GradReducer&) = delete;
+  int n_buckets() const { return int(v0_.size()); }
+  void range(int b, int& v0, int& v1) const { v0 = v0_[b]; v1 = v1_[b]; }
+  // Bucket b of grad is final on `compute`: its all-reduce is enqueued on the communication stream behind an event.
+  void bucket_ready(int b, cudaStream_t compute);
+  void reduce_all(cudaStream_t compute);       // every bucket, after the work already on `compute`
+  void wait(cudaStream_t st);                  // st waits for every bucket reduction enqueued so far
+ private:
+  Comm& comm_;
+  float* grad_;
+  int V_, D_;
+  DType dtype_;
+  void* staging_;
+  std::vector<int> v0_, v1_;
+  std::vector<cudaEvent_t> ready_;
+  cudaEvent_t done_ = nullptr;
+};
+
+}  // namespace nm

@@ -1,0 +1,494 @@
+// The three contractions of the fused linear cross-entropy as one warp-specialised, persistent tcgen05 kernel template
+// for sm_100a:
+//     logits  z[rows, V]   = x[rows, D]  W[V, D]^T      (A K-major, B K-major)   + online (max, sum exp) epilogue
+//     dX      dx[rows, D]  = n[rows, V]  W[V, D]        (A K-major, B MN-major)  + scale / bf16 / accumulate epilogue
+//     dW      dw[V, D]    += n[rows, V]^T x[rows, D]    (A MN-major, B MN-major) + f32 read-modify-write epilogue
+// They replace the reference's k_ce_logits_stats / k_ce_logits_sm90 (src/kernels/cross_entropy/ce_logits.cu:25-215,
+// ce_sm90.cu:364-495), k_ce_dgrad / k_ce_wgrad / k_ce_gemm_sm90 (ce_gemm.cu:38-392, ce_sm90.cu:558-764) and its
+// cuBLASLt plans (ce_lt.cpp:47-219).
+//
+// One CTA per SM, 192 threads: warp 0 issues the TMA loads (one elected lane), warp 1 allocates TMEM and issues the
+// UMMAs (one elected lane), warps 2-5 are the epilogue (thread = accumulator row = TMEM lane). Tiles are 128 x 256
+// (M x N) with K blocks of 64 bf16 (one 128-byte swizzle row); operands arrive by TMA into a 4-stage ring of
+// SWIZZLE_128B tiles; the f32 accumulator lives in TMEM, two buffers of 256 columns, so the epilogue of tile i runs
+// while the UMMAs of tile i + 1 are issued. Every mbarrier wait is bounded (ptx.cuh mbar_wait).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+#include <string>
+
+#include "ce_internal.hpp"
+#include "ptx.cuh"
+
+namespace nm::ce {
+namespace {
+
+using namespace nm::ptx;
+
+constexpr int BM = 128, BN = 256, BK = 64, UK = 16;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;            // 16 KiB
+constexpr int kBBytes = BN * BK * 2;            // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;  // 48 KiB
+constexpr int kBoxBytesMN = 64 * BK * 2;        // one MN-major box: 64 k-rows of 128 bytes = 8 KiB
+constexpr int kTmemCols = 512;
+constexpr int kThreads = 192;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+enum Epi : int { kEpiLogits = 0, kEpiDx = 1, kEpiDw = 2, kEpiTest = 3 };
+
+struct GemmParams {
+  int M, N, K;              // extents of this launch: accumulator rows, columns, contraction length
+  int m_off;                // first A coordinate along M (dW vocabulary range start)
+  int num_m, num_n;         // tiles
+  int m_inner;              // 1: consecutive tile indices walk M first (logits), 0: N first
+  uint32_t* status;
+  // logits
+  void* store; int64_t ldS; int store_f32;
+  float* tmax; float* tsum; int64_t ldT; float* zt; const int32_t* targets; const float* bias;
+  // dX
+  const float* scale; const void* dx_old; void* dx_out; int acc_mode; int out_f32; int64_t ldo;
+  // dW
+  float* dw; int round_bf16;
+  // test
+  float* c; int64_t ldc;
+};
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+__device__ __forceinline__ float round_bf16f(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// ---------------------------------------------------------------------------------------------- epilogues
+// One call handles the 32 accumulator columns [col0, col0 + 32) of row `grow` held in v[].
+struct LogitsRowState {
+  float m, s, zt;
+  bool hit;
+};
+
+__device__ __forceinline__ void epi_logits_chunk(const GemmParams& p, float* v, int grow, bool row_ok, int col0, int tg,
+                                                 LogitsRowState& st) {
+  const int V = p.N;
+  const int ncols = min(32, V - col0);
+  if (p.bias) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) v[j] += __ldg(p.bias + col0 + j);
+  }
+  if (p.store && row_ok) {
+    if (p.store_f32) {
+      float* o = static_cast<float*>(p.store) + int64_t(grow) * p.ldS + col0;
+      if (ncols == 32) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)     // static indices only: a runtime index would move v[] to local memory
+          if (j < ncols) o[j] = v[j];
+      }
+    } else {
+      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.store) + int64_t(grow) * p.ldS + col0;
+      if (ncols == 32) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8)
+          *reinterpret_cast<uint4*>(o + j) = make_uint4(pack2(v[j], v[j + 1]), pack2(v[j + 2], v[j + 3]),
+                                                        pack2(v[j + 4], v[j + 5]), pack2(v[j + 6], v[j + 7]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) o[j] = __float2bfloat16_rn(v[j]);
+      }
+    }
+  }
+  // online (max, sum exp): one rescale of the running sum per 32 columns
+  constexpr float kLog2e = 1.4426950408889634f;
+  float cm = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if (j < ncols) cm = fmaxf(cm, v[j]);
+  const float m_new = fmaxf(st.m, cm);
+  const float neg = -m_new * kLog2e;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    a0 += (j < ncols) ? ex2_approx(fmaf(v[j], kLog2e, neg)) : 0.f;
+    a1 += (j + 1 < ncols) ? ex2_approx(fmaf(v[j + 1], kLog2e, neg)) : 0.f;
+    a2 += (j + 2 < ncols) ? ex2_approx(fmaf(v[j + 2], kLog2e, neg)) : 0.f;
+    a3 += (j + 3 < ncols) ? ex2_approx(fmaf(v[j + 3], kLog2e, neg)) : 0.f;
+  }
+  // st.m == -inf on the first chunk: ex2(-inf) = 0 and st.s = 0
+  st.s = st.s * ex2_approx(fmaf(st.m, kLog2e, neg)) + ((a0 + a1) + (a2 + a3));
+  st.m = m_new;
+  if (tg >= col0 && tg < col0 + 32) {
+    const int jt = tg - col0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j == jt) st.zt = v[j];
+    st.hit = true;
+  }
+}
+
+__device__ __forceinline__ void epi_dx_chunk(const GemmParams& p, const float* v, int grow, int col0, float scale) {
+  const int D = p.N;
+  const int ncols = min(32, D - col0);   // D % 8 == 0, so ncols is a multiple of 8
+  if (p.out_f32) {
+    float* o = static_cast<float*>(p.dx_out) + int64_t(grow) * p.ldo + col0;
+    const float* old = static_cast<const float*>(p.dx_old) + int64_t(grow) * p.ldo + col0;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      if (j < ncols) {
+        float4 r = make_float4(v[j] * scale, v[j + 1] * scale, v[j + 2] * scale, v[j + 3] * scale);
+        if (p.acc_mode) {
+          const float4 q = *reinterpret_cast<const float4*>(old + j);
+          r.x += q.x; r.y += q.y; r.z += q.z; r.w += q.w;
+        }
+        *reinterpret_cast<float4*>(o + j) = r;
+      }
+    }
+    return;
+  }
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.dx_out) + int64_t(grow) * p.ldo + col0;
+  const __nv_bfloat16* old = static_cast<const __nv_bfloat16*>(p.dx_old) + int64_t(grow) * p.ldo + col0;
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    if (j < ncols) {
+      float r[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) r[e] = v[j + e] * scale;
+      if (p.acc_mode) {
+        const uint4 q = *reinterpret_cast<const uint4*>(old + j);
+        const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float o0 = bf_lo(qq[e]), o1 = bf_hi(qq[e]);
+          if (p.acc_mode == 1) {   // levanter: bf16(old + f32(bf16(acc)))
+            r[2 * e] = o0 + round_bf16f(r[2 * e]);
+            r[2 * e + 1] = o1 + round_bf16f(r[2 * e + 1]);
+          } else {                 // accurate: bf16(old + acc)
+            r[2 * e] = o0 + r[2 * e];
+            r[2 * e + 1] = o1 + r[2 * e + 1];
+          }
+        }
+      }
+      *reinterpret_cast<uint4*>(o + j) =
+          make_uint4(pack2(r[0], r[1]), pack2(r[2], r[3]), pack2(r[4], r[5]), pack2(r[6], r[7]));
+    }
+  }
+}
+
+__device__ __forceinline__ void epi_dw_chunk(const GemmParams& p, const float* v, int gv, int col0, float scale) {
+  const int D = p.N;
+  const int ncols = min(32, D - col0);
+  float* o = p.dw + int64_t(gv) * D + col0;
+  float4 q[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    if (4 * j < ncols) q[j] = *reinterpret_cast<const float4*>(o + 4 * j);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (4 * j < ncols) {
+      float r0 = v[4 * j] * scale, r1 = v[4 * j + 1] * scale, r2 = v[4 * j + 2] * scale, r3 = v[4 * j + 3] * scale;
+      if (p.round_bf16) { r0 = round_bf16f(r0); r1 = round_bf16f(r1); r2 = round_bf16f(r2); r3 = round_bf16f(r3); }
+      q[j].x += r0; q[j].y += r1; q[j].z += r2; q[j].w += r3;
+      *reinterpret_cast<float4*>(o + 4 * j) = q[j];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- the kernel
+template <int EPI, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;            // SWIZZLE_128B tiles need 1024-byte alignment
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t sA = base, sB = base + kStages * kABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  const uint32_t bar0 = base + kStages * kStageBytes;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.num_m * p.num_n;
+  const int k_blocks = (p.K + BK - 1) / BK;
+  auto decode = [&](int tile, int& mi, int& ni) {
+    if (p.m_inner) { mi = tile % p.num_m; ni = tile / p.num_m; }
+    else { ni = tile % p.num_n; mi = tile / p.num_n; }
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mi, ni;
+        decode(tile, mi, ni);
+        const int m0 = p.m_off + mi * BM, n0 = ni * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kErrProducerWait)) { ok = false; break; }
+          mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+          const uint32_t a_dst = sA + stage * kABytes, b_dst = sB + stage * kBBytes;
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(a_dst + j * kBoxBytesMN, &tmA, full_bar(stage), m0 + j * 64, kb * BK);
+          } else {
+            tma_load_2d(a_dst, &tmA, full_bar(stage), kb * BK, m0);
+          }
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * kBoxBytesMN, &tmB, full_bar(stage), n0 + j * 64, kb * BK);
+          } else {
+            tma_load_2d(b_dst, &tmB, full_bar(stage), kb * BK, n0);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ UMMA issuer
+      constexpr uint32_t idesc = idesc_bf16_f32(BM, BN, A_MN, B_MN);
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int b = it & 1;
+        if (!mbar_wait(tempty_bar(b), ((it >> 1) & 1u) ^ 1u, abort_flag, p.status, kErrTmemFreeWait)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + uint32_t(b * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kErrMmaWait)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_src = sA + stage * kABytes, b_src = sB + stage * kBBytes;
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            // K-major: 16 bf16 = 32 bytes further along the 128-byte row; MN-major: 16 k-rows = 2048 bytes further
+            const uint64_t ad = A_MN ? smem_desc_sw128(a_src + k * (UK * 128), kBoxBytesMN, 1024)
+                                     : smem_desc_sw128(a_src + k * (UK * 2), 16, 1024);
+            const uint64_t bd = B_MN ? smem_desc_sw128(b_src + k * (UK * 128), kBoxBytesMN, 1024)
+                                     : smem_desc_sw128(b_src + k * (UK * 2), 16, 1024);
+            umma_bf16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+          }
+          umma_commit(empty_bar(stage));   // the stage is free again once these UMMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(tfull_bar(b));   // accumulator of this tile complete
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- epilogue (warps 2-5)
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int r_local = quad * 32 + lane;
+    float scale = 1.f;
+    if constexpr (EPI == kEpiDx || EPI == kEpiDw) scale = p.scale ? __ldg(p.scale) : 1.f;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int b = it & 1;
+      int mi, ni;
+      decode(tile, mi, ni);
+      const int m0 = mi * BM, n0 = ni * BN;
+      const int grow = m0 + r_local;
+      const bool row_ok = grow < p.M;
+      if (!mbar_wait(tfull_bar(b), (it >> 1) & 1u, abort_flag, p.status, kErrEpilogueWait)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(b * BN);
+      LogitsRowState st{-INFINITY, 0.f, 0.f, false};
+      int tg = -1;
+      if constexpr (EPI == kEpiLogits) tg = row_ok ? __ldg(p.targets + grow) : -1;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;                // uniform over the CTA
+        float v[32];
+        __syncwarp();
+        tmem_ld32(taddr + uint32_t(c * 32), v);
+        tmem_ld_wait();
+        if constexpr (EPI == kEpiLogits) {
+          epi_logits_chunk(p, v, grow, row_ok, col0, tg, st);
+        } else if constexpr (EPI == kEpiDx) {
+          if (row_ok) epi_dx_chunk(p, v, grow, col0, scale);
+        } else if constexpr (EPI == kEpiDw) {
+          if (row_ok) epi_dw_chunk(p, v, p.m_off + grow, col0, scale);
+        } else {
+          if (row_ok) {
+            const int ncols = min(32, p.N - col0);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncols) p.c[int64_t(grow) * p.ldc + col0 + j] = v[j];
+          }
+        }
+      }
+      // the accumulator buffer may be overwritten by the UMMAs of the tile after next
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(b));
+      if constexpr (EPI == kEpiLogits) {
+        if (row_ok) {
+          p.tmax[int64_t(ni) * p.ldT + grow] = st.m;
+          p.tsum[int64_t(ni) * p.ldT + grow] = st.s;
+          if (st.hit) p.zt[grow] = st.zt;
+        }
+      }
+    }
+  }
+
+  // -------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    if (*abort_flag) __nanosleep(200000);   // an expired wait: let copies and UMMAs in flight land before TMEM goes
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static std::once_flag once;
+  static EncodeFn fn = nullptr;
+  static cudaError_t err = cudaSuccess;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (err == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeFn>(p);
+  });
+  if (!fn) {
+    cudaGetLastError();
+    throw DeviceError(std::string("fused CE: cuTensorMapEncodeTiled is not available from the CUDA driver (") +
+                      cudaGetErrorString(err) + "); this library needs an sm_100a device and has no other path");
+  }
+  return fn;
+}
+
+// bf16 matrix with `inner` contiguous elements per row, `outer` rows, row pitch ld elements; box = (box_inner, box_outer)
+CUtensorMap make_tmap(const void* base, uint64_t inner, uint64_t outer, int64_t ld, uint32_t box_inner,
+                      uint32_t box_outer) {
+  NM_REQUIRE(reinterpret_cast<uintptr_t>(base) % 16 == 0, "fused CE: a TMA operand must be 16-byte aligned");
+  NM_REQUIRE((ld * 2) % 16 == 0, "fused CE: a TMA operand's row pitch must be a multiple of 16 bytes");
+  NM_REQUIRE(inner > 0 && outer > 0, "fused CE: empty TMA operand");
+  CUtensorMap m;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw DeviceError("fused CE: cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(r)) + " (inner " +
+                      std::to_string(inner) + ", outer " + std::to_string(outer) + ", ld " + std::to_string(ld) + ")");
+  return m;
+}
+// K-major operand [rows, K]: box = 64 k x `rows_per_box` rows. MN-major operand [K, MN]: box = 64 mn x 64 k.
+CUtensorMap tmap_kmajor(const void* base, int64_t rows, int64_t K, int64_t ld, int rows_per_box) {
+  return make_tmap(base, uint64_t(K), uint64_t(rows), ld, BK, uint32_t(rows_per_box));
+}
+CUtensorMap tmap_mnmajor(const void* base, int64_t K, int64_t MN, int64_t ld) {
+  return make_tmap(base, uint64_t(MN), uint64_t(K), ld, 64, BK);
+}
+
+template <int EPI, bool A_MN, bool B_MN>
+void launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
+  auto kernel = k_ce_umma<EPI, A_MN, B_MN>;
+  NM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  const int tiles = p.num_m * p.num_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kernel<<<grid, kThreads, kSmemBytes, st>>>(ta, tb, p);
+  NM_CUDA(cudaGetLastError());
+}
+
+}  // namespace
+
+void launch_logits(const LogitsArgs& a, cudaStream_t st) {
+  if (a.rows <= 0) return;
+  GemmParams p{};
+  p.M = a.rows; p.N = a.V; p.K = a.D; p.m_off = 0;
+  p.num_m = (a.rows + BM - 1) / BM; p.num_n = (a.V + BN - 1) / BN; p.m_inner = 1;
+  p.status = a.status;
+  p.store = a.store; p.ldS = a.ldS; p.store_f32 = a.store_f32;
+  p.tmax = a.tmax; p.tsum = a.tsum; p.ldT = a.ldT; p.zt = a.zt; p.targets = a.targets; p.bias = a.bias;
+  const CUtensorMap ta = tmap_kmajor(a.x, a.rows, a.D, a.D, BM);
+  const CUtensorMap tb = tmap_kmajor(a.w, a.V, a.D, a.D, BN);
+  launch<kEpiLogits, false, false>(ta, tb, p, st);
+}
+
+void launch_dgrad(const DgradArgs& a, cudaStream_t st) {
+  if (a.rows <= 0) return;
+  GemmParams p{};
+  p.M = a.rows; p.N = a.D; p.K = a.V; p.m_off = 0;
+  p.num_m = (a.rows + BM - 1) / BM; p.num_n = (a.D + BN - 1) / BN; p.m_inner = 0;
+  p.status = a.status;
+  p.scale = a.scale; p.dx_old = a.dx_old; p.dx_out = a.dx_out; p.acc_mode = a.dx_old ? a.acc_mode : 0;
+  p.out_f32 = a.out_f32; p.ldo = a.D;
+  const CUtensorMap ta = tmap_kmajor(a.n, a.rows, a.V, a.ldn, BM);
+  const CUtensorMap tb = tmap_mnmajor(a.w, a.V, a.D, a.ldw);
+  launch<kEpiDx, false, true>(ta, tb, p, st);
+}
+
+void launch_wgrad(const WgradArgs& a, cudaStream_t st) {
+  if (a.rows <= 0 || a.v1 <= a.v0) return;
+  NM_REQUIRE(a.v0 % BM == 0, "fused CE: a dW vocabulary range must start on a multiple of 128");
+  GemmParams p{};
+  p.M = a.v1 - a.v0; p.N = a.D; p.K = a.rows; p.m_off = a.v0;
+  p.num_m = (p.M + BM - 1) / BM; p.num_n = (a.D + BN - 1) / BN; p.m_inner = 0;
+  p.status = a.status;
+  p.scale = a.scale; p.dw = a.dw; p.round_bf16 = a.round_bf16;
+  const CUtensorMap ta = tmap_mnmajor(a.n, a.rows, a.V, a.ldn);
+  const CUtensorMap tb = tmap_mnmajor(a.x, a.rows, a.D, a.ldx);
+  launch<kEpiDw, true, true>(ta, tb, p, st);
+}
+
+void launch_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,
+                      int N, int K, uint32_t* status, cudaStream_t st) {
+  NM_REQUIRE(kind >= 0 && kind <= 2, "test gemm: kind 0, 1 or 2");
+  NM_REQUIRE(M > 0 && N > 0 && K > 0, "test gemm: M, N, K > 0");
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.m_off = 0;
+  p.num_m = (M + BM - 1) / BM; p.num_n = (N + BN - 1) / BN; p.m_inner = 0;
+  p.status = status; p.c = c; p.ldc = ldc;
+  if (kind == 0) {
+    launch<kEpiTest, false, false>(tmap_kmajor(a, M, K, lda, BM), tmap_kmajor(b, N, K, ldb, BN), p, st);
+  } else if (kind == 1) {
+    launch<kEpiTest, false, true>(tmap_kmajor(a, M, K, lda, BM), tmap_mnmajor(b, K, N, ldb), p, st);
+  } else {
+    launch<kEpiTest, true, true>(tmap_mnmajor(a, K, M, lda), tmap_mnmajor(b, K, N, ldb), p, st);
+  }
+}
+
+}  // namespace nm::ce

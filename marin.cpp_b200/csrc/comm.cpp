@@ -1,0 +1,144 @@
+// NCCL communicator and the bucketed dW reducer (include/marincpp/comm.hpp). NCCL is resolved at run time from the
+// libnccl.so.2 already loaded in the process (the one torch.distributed uses) or, failing that, the system one, so the
+// library carries no link-time dependency on a particular NCCL build.
+#include "marincpp/comm.hpp"
+
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <mutex>
+#include <string>
+
+#include "ce_internal.hpp"
+
+namespace nm {
+namespace {
+
+struct NcclApi {
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+  std::string error;
+};
+
+const NcclApi& nccl() {
+  static NcclApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) {
+      api.error = std::string("libnccl.so.2 could not be loaded: ") + dlerror();
+      return;
+    }
+    auto sym = [&](const char* name) -> void* {
+      void* p = dlsym(h, name);
+      if (!p && api.error.empty()) api.error = std::string("libnccl.so.2 lacks ") + name;
+      return p;
+    };
+    api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+    api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+    api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+    api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
+    api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+  });
+  if (!api.error.empty()) throw DeviceError("comm: " + api.error);
+  return api;
+}
+
+}  // namespace
+
+void nccl_check(int err, const char* expr, const char* where) {
+  if (err == 0) return;
+  const char* s = nccl().GetErrorString ? nccl().GetErrorString(static_cast<ncclResult_t>(err)) : "?";
+  throw DeviceError(std::string(where) + ": " + expr + " failed: NCCL error " + std::to_string(err) + " (" + s + ")");
+}
+
+static_assert(sizeof(ncclUniqueId) == 128, "the C ABI passes the NCCL unique id as 128 bytes");
+
+void Comm::unique_id(void* id128_host) {
+  NM_REQUIRE(id128_host, "comm: id buffer required");
+  ncclUniqueId id;
+  NM_NCCL(nccl().GetUniqueId(&id));
+  std::memcpy(id128_host, &id, sizeof(id));
+}
+
+Comm::Comm(const void* id128_host, int nranks, int rank) : nranks_(nranks), rank_(rank) {
+  NM_REQUIRE(id128_host, "comm: id required");
+  NM_REQUIRE(nranks >= 1 && nranks <= kMaxGpus && rank >= 0 && rank < nranks, "comm: 1 <= nranks <= 8, 0 <= rank < nranks");
+  NM_CUDA(cudaGetDevice(&device_));
+  ncclUniqueId id;
+  std::memcpy(&id, id128_host, sizeof(id));
+  ncclComm_t c = nullptr;
+  NM_NCCL(nccl().CommInitRank(&c, nranks, id, rank));
+  comm_ = c;
+  NM_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+}
+
+Comm::~Comm() {
+  if (stream_) cudaStreamDestroy(stream_);
+  if (comm_) nccl().CommDestroy(static_cast<ncclComm_t>(comm_));
+}
+
+void Comm::allreduce_sum(void* buf, int64_t n, DType dt, cudaStream_t st) {
+  NM_REQUIRE(dt == DType::f32 || dt == DType::bf16, "comm: all-reduce of f32 or bf16");
+  if (n <= 0) return;
+  NM_NCCL(nccl().AllReduce(buf, buf, size_t(n), dt == DType::f32 ? ncclFloat32 : ncclBfloat16, ncclSum,
+                           static_cast<ncclComm_t>(comm_), st));
+}
+
+GradReducer::GradReducer(Comm& comm, float* grad, int V, int D, int n_buckets, DType reduce_dtype, void* staging)
+    : comm_(comm), grad_(grad), V_(V), D_(D), dtype_(reduce_dtype), staging_(staging) {
+  NM_REQUIRE(grad && V > 0 && D > 0, "grad reducer: grad, V, D required");
+  NM_REQUIRE(n_buckets >= 1 && n_buckets <= 64, "grad reducer: 1 <= n_buckets <= 64");
+  NM_REQUIRE(reduce_dtype == DType::f32 || (reduce_dtype == DType::bf16 && staging),
+             "grad reducer: reduce dtype f32, or bf16 with a staging buffer");
+  const int tiles = (V + ce::kTileM - 1) / ce::kTileM;
+  const int nb = n_buckets < tiles ? n_buckets : tiles;
+  int t0 = 0;
+  for (int b = 0; b < nb; ++b) {
+    const int t1 = t0 + (tiles - t0) / (nb - b);
+    v0_.push_back(t0 * ce::kTileM);
+    v1_.push_back(t1 * ce::kTileM < V ? t1 * ce::kTileM : V);
+    t0 = t1;
+  }
+  v1_.back() = V;
+  ready_.resize(v0_.size());
+  for (auto& e : ready_) NM_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  NM_CUDA(cudaEventCreateWithFlags(&done_, cudaEventDisableTiming));
+  NM_CUDA(cudaEventRecord(done_, comm_.stream()));
+}
+
+GradReducer::~GradReducer() {
+  for (auto e : ready_) if (e) cudaEventDestroy(e);
+  if (done_) cudaEventDestroy(done_);
+}
+
+void GradReducer::bucket_ready(int b, cudaStream_t compute) {
+  NM_REQUIRE(b >= 0 && b < n_buckets(), "grad reducer: bucket index");
+  cudaStream_t cs = comm_.stream();
+  NM_CUDA(cudaEventRecord(ready_[b], compute));
+  NM_CUDA(cudaStreamWaitEvent(cs, ready_[b], 0));
+  float* g = grad_ + int64_t(v0_[b]) * D_;
+  const int64_t n = int64_t(v1_[b] - v0_[b]) * D_;
+  if (dtype_ == DType::f32) {
+    comm_.allreduce_sum(g, n, DType::f32, cs);
+  } else {
+    uint16_t* s = static_cast<uint16_t*>(staging_) + int64_t(v0_[b]) * D_;
+    ce::launch_f32_to_bf16(g, s, n, cs);
+    comm_.allreduce_sum(s, n, DType::bf16, cs);
+    ce::launch_bf16_to_f32(s, g, n, cs);
+  }
+  NM_CUDA(cudaEventRecord(done_, cs));
+}
+
+void GradReducer::reduce_all(cudaStream_t compute) {
+  for (int b = 0; b < n_buckets(); ++b) bucket_ready(b, compute);
+}
+
+void GradReducer::wait(cudaStream_t st) { NM_CUDA(cudaStreamWaitEvent(st, done_, 0)); }
+
+}  // namespace nm
