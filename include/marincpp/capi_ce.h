@@ -66,6 +66,19 @@ int nm_ce_profile_read(double* ms_host /*[6]*/, int* launches_host /*[6]*/);
 int nm_ce_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,
                     int N, int K, uint32_t* status, void* stream);
 
+/* Forward only (per-token loss, lse, per-chunk loss sums; bf16 x and W) WITHOUT a caller workspace and without any
+ * allocation: the scratch of one chunk lives in a 16 MiB device array built into the library (held by every GPU that
+ * loads it). This entry point has no counterpart in the reference. It is for callers that cannot allocate: a trainer
+ * whose single up-front arena has no region planned for an extra evaluation or probe call, or a thread that runs while
+ * a stream capture is open, when cudaMalloc is not permitted. Same results as nm_fused_linear_ce_ex with
+ * forward_only = 1 and the same chunk_rows. Needs 256 + 8 ceil(V / 256) chunk_rows + 12 chunk_rows bytes of scratch
+ * (chunk_rows <= 4096 at V = 128256); a larger request returns NM_ERR_INVALID. The first call on a device resolves
+ * the array's device address: make it before any stream capture. All calls on a GPU share the array: calls whose
+ * kernels may overlap on the device race and must be serialised by the caller. lse and loss_partial may be NULL. */
+int nm_ce_forward_noalloc(const void* x, const void* w, const int32_t* targets, const float* weight, float* loss_tok,
+                          float* lse, float* loss_partial, int64_t T, int D, int V, int chunk_rows,
+                          float z_loss_weight, int32_t ignore_index, void* stream);
+
 /* ---- data-parallel dW reduction over NCCL (the role of the reference's include/marincpp/comm.hpp:22-58 GradReducer
  *      and of src/train/trainer.cpp:50,139): one communicator per process (one process per GPU) ------------------- */
 int nm_comm_unique_id(void* id128_host);                       /* rank 0: 128 bytes to broadcast to the other ranks */
