@@ -190,10 +190,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--chunk", type=int, default=16384)
     ap.add_argument("--buckets", type=int, default=8)
+    ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (small cases for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg")
     args = ap.parse_args()
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.tokens > 0:
+        cfg["T"] = args.tokens
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -396,7 +399,8 @@ def main():
         "metric": "fused_ce_fwd_bwd_tokens_per_s", "value": tokens / (ms_total * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD[args.config], "tokens_per_gpu": R * T, "hidden": D, "vocab": V,
+        "config": {"workload": WORKLOAD[args.config] + (f" [tokens overridden to {T}]" if args.tokens > 0 else ""),
+                   "tokens_per_gpu": R * T, "hidden": D, "vocab": V,
                    "chunk_rows": chunk, "readouts": R, "parallelism": f"dp{world} (rows sharded, W replicated)",
                    "dw_allreduce": (f"{cfg['reduce']}, {args.buckets} buckets, overlapped with the last dX" if world > 1
                                     else "none (1 GPU)"),

@@ -11,7 +11,11 @@
 // UMMAs (one elected lane), warps 2-5 are the epilogue (thread = accumulator row = TMEM lane). Tiles are 128 x 256
 // (M x N) with K blocks of 64 bf16 (one 128-byte swizzle row); operands arrive by TMA into a 4-stage ring of
 // SWIZZLE_128B tiles; the f32 accumulator lives in TMEM, two buffers of 256 columns, so the epilogue of tile i runs
-// while the UMMAs of tile i + 1 are issued. Every mbarrier wait is bounded (ptx.cuh mbar_wait).
+// while the UMMAs of tile i + 1 are issued. TMEM loads are software-pipelined (the next 32 columns load while the
+// current 32 are processed). The bf16 logits store and the f32 dW accumulation leave through shared memory: each
+// epilogue warp packs its 32 rows into a 128-byte-swizzled 4 KiB staging tile and one lane issues a TMA store (logits)
+// or a TMA reduce-add (dW += tile, the addition done at L2), so global traffic is full lines and the dW update needs no
+// read. Every mbarrier wait is bounded (ptx.cuh mbar_wait).
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -35,9 +39,14 @@ constexpr int kStageBytes = kABytes + kBBytes;  // 48 KiB
 constexpr int kBoxBytesMN = 64 * BK * 2;        // one MN-major box: 64 k-rows of 128 bytes = 8 KiB
 constexpr int kTmemCols = 512;
 constexpr int kThreads = 192;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-
 enum Epi : int { kEpiLogits = 0, kEpiDx = 1, kEpiDw = 2, kEpiTest = 3 };
+
+// epilogue staging: 4 warps x 2 buffers x (32 rows x 128 bytes), only for the epilogues that leave through TMA
+constexpr int kEpiBufBytes = 32 * 128;
+__host__ __device__ constexpr int epi_stage_bytes(int epi) { return (epi == kEpiLogits || epi == kEpiDw) ? 4 * 2 * kEpiBufBytes : 0; }
+constexpr int smem_bytes(int epi) {
+  return kStages * kStageBytes + epi_stage_bytes(epi) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+}
 
 struct GemmParams {
   int M, N, K;              // extents of this launch: accumulator rows, columns, contraction length
@@ -80,29 +89,15 @@ __device__ __forceinline__ void epi_logits_chunk(const GemmParams& p, float* v, 
     for (int j = 0; j < 32; ++j)
       if (j < ncols) v[j] += __ldg(p.bias + col0 + j);
   }
-  if (p.store && row_ok) {
-    if (p.store_f32) {
-      float* o = static_cast<float*>(p.store) + int64_t(grow) * p.ldS + col0;
-      if (ncols == 32) {
+  if (p.store && p.store_f32 && row_ok) {   // f32 store: direct (the bf16 store leaves through the staging tile)
+    float* o = static_cast<float*>(p.store) + int64_t(grow) * p.ldS + col0;
+    if (ncols == 32) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)     // static indices only: a runtime index would move v[] to local memory
-          if (j < ncols) o[j] = v[j];
-      }
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
     } else {
-      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.store) + int64_t(grow) * p.ldS + col0;
-      if (ncols == 32) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 8)
-          *reinterpret_cast<uint4*>(o + j) = make_uint4(pack2(v[j], v[j + 1]), pack2(v[j + 2], v[j + 3]),
-                                                        pack2(v[j + 4], v[j + 5]), pack2(v[j + 6], v[j + 7]));
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < ncols) o[j] = __float2bfloat16_rn(v[j]);
-      }
+      for (int j = 0; j < 32; ++j)     // static indices only: a runtime index would move v[] to local memory
+        if (j < ncols) o[j] = v[j];
     }
   }
   // online (max, sum exp): one rescale of the running sum per 32 columns
@@ -181,36 +176,39 @@ __device__ __forceinline__ void epi_dx_chunk(const GemmParams& p, const float* v
   }
 }
 
-__device__ __forceinline__ void epi_dw_chunk(const GemmParams& p, const float* v, int gv, int col0, float scale) {
-  const int D = p.N;
-  const int ncols = min(32, D - col0);
-  float* o = p.dw + int64_t(gv) * D + col0;
-  float4 q[8];
+// Staging writers: this lane's row of a 32-row x 128-byte tile, 16-byte pieces XOR-swizzled with the row as
+// SWIZZLE_128B expects (piece j of row r at r * 128 + ((j ^ (r & 7)) << 4); the tile is 1024-byte aligned).
+__device__ __forceinline__ void stage_bf16_half(uint32_t buf, int lane, int half, const float* v) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j)
-    if (4 * j < ncols) q[j] = *reinterpret_cast<const float4*>(o + 4 * j);
+  for (int q = 0; q < 4; ++q) {
+    const int j = half * 4 + q;
+    st_shared_v4(buf + lane * 128 + ((j ^ (lane & 7)) << 4), pack2(v[8 * q], v[8 * q + 1]),
+                 pack2(v[8 * q + 2], v[8 * q + 3]), pack2(v[8 * q + 4], v[8 * q + 5]), pack2(v[8 * q + 6], v[8 * q + 7]));
+  }
+}
+__device__ __forceinline__ void stage_f32_row(uint32_t buf, int lane, const float* v, float scale, bool round_bf16) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    if (4 * j < ncols) {
-      float r0 = v[4 * j] * scale, r1 = v[4 * j + 1] * scale, r2 = v[4 * j + 2] * scale, r3 = v[4 * j + 3] * scale;
-      if (p.round_bf16) { r0 = round_bf16f(r0); r1 = round_bf16f(r1); r2 = round_bf16f(r2); r3 = round_bf16f(r3); }
-      q[j].x += r0; q[j].y += r1; q[j].z += r2; q[j].w += r3;
-      *reinterpret_cast<float4*>(o + 4 * j) = q[j];
-    }
+    float r0 = v[4 * j] * scale, r1 = v[4 * j + 1] * scale, r2 = v[4 * j + 2] * scale, r3 = v[4 * j + 3] * scale;
+    if (round_bf16) { r0 = round_bf16f(r0); r1 = round_bf16f(r1); r2 = round_bf16f(r2); r3 = round_bf16f(r3); }
+    st_shared_v4(buf + lane * 128 + ((j ^ (lane & 7)) << 4), __float_as_uint(r0), __float_as_uint(r1),
+                 __float_as_uint(r2), __float_as_uint(r3));
   }
 }
 
 // ---------------------------------------------------------------------------------------------- the kernel
 template <int EPI, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
-k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+          const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;            // SWIZZLE_128B tiles need 1024-byte alignment
   uint8_t* smem = smem_raw + (base - raw);
   const uint32_t sA = base, sB = base + kStages * kABytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-  const uint32_t bar0 = base + kStages * kStageBytes;
+  const uint32_t sEpi = base + kStages * kStageBytes;      // epilogue staging tiles (1024-byte aligned)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + epi_stage_bytes(EPI));
+  const uint32_t bar0 = sEpi + epi_stage_bytes(EPI);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
@@ -226,6 +224,7 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    if constexpr (epi_stage_bytes(EPI) > 0) prefetch_tmap(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -309,8 +308,11 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     // -------------------------------------------------------------------- epilogue (warps 2-5)
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
     const int r_local = quad * 32 + lane;
+    const uint32_t stg = sEpi + uint32_t(warp - 2) * 2 * kEpiBufBytes;   // this warp's two staging tiles
+    uint32_t n_bulk = 0;                        // bulk groups this warp has issued (staging tile = n_bulk & 1)
     float scale = 1.f;
     if constexpr (EPI == kEpiDx || EPI == kEpiDw) scale = p.scale ? __ldg(p.scale) : 1.f;
+    const bool staged_store = EPI == kEpiLogits && p.store != nullptr && !p.store_f32;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int b = it & 1;
@@ -319,26 +321,54 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       const int m0 = mi * BM, n0 = ni * BN;
       const int grow = m0 + r_local;
       const bool row_ok = grow < p.M;
+      const bool warp_rows_ok = m0 + quad * 32 < p.M;          // any row of this warp inside the matrix
       if (!mbar_wait(tfull_bar(b), (it >> 1) & 1u, abort_flag, p.status, kErrEpilogueWait)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(b * BN);
       LogitsRowState st{-INFINITY, 0.f, 0.f, false};
       int tg = -1;
       if constexpr (EPI == kEpiLogits) tg = row_ok ? __ldg(p.targets + grow) : -1;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+
+      // one 32-column chunk held in v[]
+      auto process = [&](float* v, int c) {
         const int col0 = n0 + c * 32;
-        if (col0 >= p.N) break;                // uniform over the CTA
-        float v[32];
-        __syncwarp();
-        tmem_ld32(taddr + uint32_t(c * 32), v);
-        tmem_ld_wait();
+        if (col0 >= p.N) return;               // uniform over the CTA
         if constexpr (EPI == kEpiLogits) {
           epi_logits_chunk(p, v, grow, row_ok, col0, tg, st);
+          if (staged_store && warp_rows_ok) {
+            // two chunks fill one 64-column staging tile; the tile's previous TMA store must have read it
+            const uint32_t buf = stg + (n_bulk & 1u) * kEpiBufBytes;
+            if ((c & 1) == 0) {
+              if (lane == 0) bulk_wait_read<1>();
+              __syncwarp();
+            }
+            stage_bf16_half(buf, lane, c & 1, v);
+            if ((c & 1) == 1 || col0 + 32 >= p.N) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {                 // rows and columns beyond the matrix are clipped by the tensor map
+                tma_store_2d(&tmC, buf, n0 + (c >> 1) * 64, m0 + quad * 32);
+                bulk_commit();
+              }
+              ++n_bulk;
+            }
+          }
         } else if constexpr (EPI == kEpiDx) {
           if (row_ok) epi_dx_chunk(p, v, grow, col0, scale);
         } else if constexpr (EPI == kEpiDw) {
-          if (row_ok) epi_dw_chunk(p, v, p.m_off + grow, col0, scale);
+          if (warp_rows_ok) {
+            const uint32_t buf = stg + (n_bulk & 1u) * kEpiBufBytes;
+            if (lane == 0) bulk_wait_read<1>();
+            __syncwarp();
+            stage_f32_row(buf, lane, v, scale, p.round_bf16 != 0);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {                   // rows beyond the vocabulary are clipped by the tensor map
+              tma_reduce_add_2d(&tmC, buf, col0, p.m_off + m0 + quad * 32);
+              bulk_commit();
+            }
+            ++n_bulk;
+          }
         } else {
           if (row_ok) {
             const int ncols = min(32, p.N - col0);
@@ -347,6 +377,24 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
               if (j < ncols) p.c[int64_t(grow) * p.ldc + col0 + j] = v[j];
           }
         }
+      };
+
+      // software pipeline over the 8 chunks: the next chunk's TMEM load is in flight while this one is processed
+      float va[32], vb[32];
+      __syncwarp();
+      tmem_ld32(taddr, va);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c += 2) {
+        tmem_ld_wait(va);
+        __syncwarp();
+        tmem_ld32(taddr + uint32_t((c + 1) * 32), vb);
+        process(va, c);
+        tmem_ld_wait(vb);
+        if (c + 2 < BN / 32) {
+          __syncwarp();
+          tmem_ld32(taddr + uint32_t((c + 2) * 32), va);
+        }
+        process(vb, c + 1);
       }
       // the accumulator buffer may be overwritten by the UMMAs of the tile after next
       tc_fence_before();
@@ -359,6 +407,10 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           if (st.hit) p.zt[grow] = st.zt;
         }
       }
+    }
+    if constexpr (epi_stage_bytes(EPI) > 0) {
+      if (lane == 0) bulk_wait<0>();           // every staged store / reduction has been performed
+      __syncwarp();
     }
   }
 
@@ -398,16 +450,17 @@ EncodeFn encode_fn() {
 
 // bf16 matrix with `inner` contiguous elements per row, `outer` rows, row pitch ld elements; box = (box_inner, box_outer)
 CUtensorMap make_tmap(const void* base, uint64_t inner, uint64_t outer, int64_t ld, uint32_t box_inner,
-                      uint32_t box_outer) {
+                      uint32_t box_outer, bool f32 = false) {
+  const int esz = f32 ? 4 : 2;
   NM_REQUIRE(reinterpret_cast<uintptr_t>(base) % 16 == 0, "fused CE: a TMA operand must be 16-byte aligned");
-  NM_REQUIRE((ld * 2) % 16 == 0, "fused CE: a TMA operand's row pitch must be a multiple of 16 bytes");
+  NM_REQUIRE((ld * esz) % 16 == 0, "fused CE: a TMA operand's row pitch must be a multiple of 16 bytes");
   NM_REQUIRE(inner > 0 && outer > 0, "fused CE: empty TMA operand");
   CUtensorMap m;
   const cuuint64_t dims[2] = {inner, outer};
-  const cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
+  const cuuint64_t strides[1] = {cuuint64_t(ld) * esz};
   const cuuint32_t box[2] = {box_inner, box_outer};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+  const CUresult r = encode_fn()(&m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
@@ -423,13 +476,21 @@ CUtensorMap tmap_mnmajor(const void* base, int64_t K, int64_t MN, int64_t ld) {
   return make_tmap(base, uint64_t(MN), uint64_t(K), ld, 64, BK);
 }
 
+// epilogue staging tile as a tensor-map box: 32 rows x 128 bytes (64 bf16 or 32 f32)
+CUtensorMap tmap_epilogue(void* base, int64_t rows, int64_t cols, int64_t ld, bool f32) {
+  return make_tmap(base, uint64_t(cols), uint64_t(rows), ld, f32 ? 32 : 64, 32, f32);
+}
+
 template <int EPI, bool A_MN, bool B_MN>
-void launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
+void launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+            cudaStream_t st) {
   auto kernel = k_ce_umma<EPI, A_MN, B_MN>;
-  NM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  constexpr int kSmem = smem_bytes(EPI);
+  static_assert(kSmem <= 232448, "dynamic shared memory beyond the 227 KiB a CTA may use");
+  NM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
   const int tiles = p.num_m * p.num_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kernel<<<grid, kThreads, kSmemBytes, st>>>(ta, tb, p);
+  kernel<<<grid, kThreads, kSmem, st>>>(ta, tb, tc, p);
   NM_CUDA(cudaGetLastError());
 }
 
@@ -445,7 +506,9 @@ void launch_logits(const LogitsArgs& a, cudaStream_t st) {
   p.tmax = a.tmax; p.tsum = a.tsum; p.ldT = a.ldT; p.zt = a.zt; p.targets = a.targets; p.bias = a.bias;
   const CUtensorMap ta = tmap_kmajor(a.x, a.rows, a.D, a.D, BM);
   const CUtensorMap tb = tmap_kmajor(a.w, a.V, a.D, a.D, BN);
-  launch<kEpiLogits, false, false>(ta, tb, p, st);
+  // the bf16 store leaves by TMA; without one (forward only, f32 store) the map is unused
+  const CUtensorMap tc = (a.store && !a.store_f32) ? tmap_epilogue(a.store, a.rows, a.V, a.ldS, false) : ta;
+  launch<kEpiLogits, false, false>(ta, tb, tc, p, st);
 }
 
 void launch_dgrad(const DgradArgs& a, cudaStream_t st) {
@@ -458,12 +521,13 @@ void launch_dgrad(const DgradArgs& a, cudaStream_t st) {
   p.out_f32 = a.out_f32; p.ldo = a.D;
   const CUtensorMap ta = tmap_kmajor(a.n, a.rows, a.V, a.ldn, BM);
   const CUtensorMap tb = tmap_mnmajor(a.w, a.V, a.D, a.ldw);
-  launch<kEpiDx, false, true>(ta, tb, p, st);
+  launch<kEpiDx, false, true>(ta, tb, ta, p, st);
 }
 
 void launch_wgrad(const WgradArgs& a, cudaStream_t st) {
   if (a.rows <= 0 || a.v1 <= a.v0) return;
-  NM_REQUIRE(a.v0 % BM == 0, "fused CE: a dW vocabulary range must start on a multiple of 128");
+  NM_REQUIRE(a.v0 % BM == 0 && (a.v1 % BM == 0 || a.v1 == a.V) && a.v1 <= a.V,
+             "fused CE: a dW vocabulary range must start and end on multiples of 128 (or end at V)");
   GemmParams p{};
   p.M = a.v1 - a.v0; p.N = a.D; p.K = a.rows; p.m_off = a.v0;
   p.num_m = (p.M + BM - 1) / BM; p.num_n = (a.D + BN - 1) / BN; p.m_inner = 0;
@@ -471,7 +535,8 @@ void launch_wgrad(const WgradArgs& a, cudaStream_t st) {
   p.scale = a.scale; p.dw = a.dw; p.round_bf16 = a.round_bf16;
   const CUtensorMap ta = tmap_mnmajor(a.n, a.rows, a.V, a.ldn);
   const CUtensorMap tb = tmap_mnmajor(a.x, a.rows, a.D, a.ldx);
-  launch<kEpiDw, true, true>(ta, tb, p, st);
+  const CUtensorMap tc = tmap_epilogue(a.dw, a.V, a.D, a.D, true);
+  launch<kEpiDw, true, true>(ta, tb, tc, p, st);
 }
 
 void launch_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,
@@ -483,11 +548,14 @@ void launch_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64
   p.num_m = (M + BM - 1) / BM; p.num_n = (N + BN - 1) / BN; p.m_inner = 0;
   p.status = status; p.c = c; p.ldc = ldc;
   if (kind == 0) {
-    launch<kEpiTest, false, false>(tmap_kmajor(a, M, K, lda, BM), tmap_kmajor(b, N, K, ldb, BN), p, st);
+    const CUtensorMap ta = tmap_kmajor(a, M, K, lda, BM);
+    launch<kEpiTest, false, false>(ta, tmap_kmajor(b, N, K, ldb, BN), ta, p, st);
   } else if (kind == 1) {
-    launch<kEpiTest, false, true>(tmap_kmajor(a, M, K, lda, BM), tmap_mnmajor(b, K, N, ldb), p, st);
+    const CUtensorMap ta = tmap_kmajor(a, M, K, lda, BM);
+    launch<kEpiTest, false, true>(ta, tmap_mnmajor(b, K, N, ldb), ta, p, st);
   } else {
-    launch<kEpiTest, true, true>(tmap_mnmajor(a, K, M, lda), tmap_mnmajor(b, K, N, ldb), p, st);
+    const CUtensorMap ta = tmap_mnmajor(a, K, M, lda);
+    launch<kEpiTest, true, true>(ta, tmap_mnmajor(b, K, N, ldb), ta, p, st);
   }
 }
 
