@@ -90,6 +90,9 @@ int nm_comm_allreduce_f32(void* comm, float* buf, int64_t n, void* stream);     
  * owned), all-reduced in bf16 and cast back. */
 int nm_grad_reducer_create(void* comm, float* grad, int V, int D, int n_buckets, int reduce_dtype, void* staging,
                            void** reducer_out);
+/* the vocabulary ranges such a reducer uses (host arithmetic only): v0/v1 hold up to n_buckets entries, *n_out the
+ * number of buckets actually made (whole 128-row tiles; fewer buckets than asked when V has fewer tiles) */
+int nm_grad_bucket_ranges(int V, int n_buckets, int* v0_host, int* v1_host, int* n_out);
 int nm_grad_reducer_destroy(void* reducer);
 /* all buckets, in order, after the work already on `stream` (no overlap: what trainer.cpp:139 does) */
 int nm_grad_reducer_reduce_all(void* reducer, void* stream);

@@ -33,6 +33,10 @@ class Comm {
   int nranks_ = 1, rank_ = 0, device_ = 0;
 };
 
+// Splits [0, V) into at most n_buckets contiguous ranges of whole 128-row tiles (the last ends at V), sizes as even as
+// the tile count allows. Returns the number of buckets (pure host arithmetic).
+int grad_bucket_ranges(int V, int n_buckets, std::vector<int>& v0, std::vector<int>& v1);
+
 class GradReducer {
  public:
   // grad [V, D] f32; n_buckets contiguous vocabulary ranges whose sizes are multiples of 128 rows (the last takes the

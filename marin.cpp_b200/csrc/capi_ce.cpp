@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 
 #include <string>
+#include <vector>
 
 #include "capi_util.hpp"
 #include "ce_internal.hpp"
@@ -223,6 +224,14 @@ int nm_grad_reducer_create(void* comm, float* grad, int V, int D, int n_buckets,
     NM_REQUIRE(comm && reducer_out, "nm_grad_reducer_create: comm and reducer_out required");
     *reducer_out = new nm::GradReducer(*static_cast<nm::Comm*>(comm), grad, V, D, n_buckets,
                                        dtype_of(reduce_dtype, "reduce_dtype"), staging);
+  });
+}
+int nm_grad_bucket_ranges(int V, int n_buckets, int* v0_host, int* v1_host, int* n_out) {
+  return nm::capi_call([&] {
+    NM_REQUIRE(v0_host && v1_host && n_out, "nm_grad_bucket_ranges: output arrays required");
+    std::vector<int> a, b;
+    *n_out = nm::grad_bucket_ranges(V, n_buckets, a, b);
+    for (int i = 0; i < *n_out; ++i) { v0_host[i] = a[size_t(i)]; v1_host[i] = b[size_t(i)]; }
   });
 }
 int nm_grad_reducer_destroy(void* reducer) {

@@ -90,22 +90,30 @@ void Comm::allreduce_sum(void* buf, int64_t n, DType dt, cudaStream_t st) {
                            static_cast<ncclComm_t>(comm_), st));
 }
 
-GradReducer::GradReducer(Comm& comm, float* grad, int V, int D, int n_buckets, DType reduce_dtype, void* staging)
-    : comm_(comm), grad_(grad), V_(V), D_(D), dtype_(reduce_dtype), staging_(staging) {
-  NM_REQUIRE(grad && V > 0 && D > 0, "grad reducer: grad, V, D required");
+int grad_bucket_ranges(int V, int n_buckets, std::vector<int>& v0, std::vector<int>& v1) {
+  NM_REQUIRE(V > 0, "grad reducer: V > 0");
   NM_REQUIRE(n_buckets >= 1 && n_buckets <= 64, "grad reducer: 1 <= n_buckets <= 64");
-  NM_REQUIRE(reduce_dtype == DType::f32 || (reduce_dtype == DType::bf16 && staging),
-             "grad reducer: reduce dtype f32, or bf16 with a staging buffer");
   const int tiles = (V + ce::kTileM - 1) / ce::kTileM;
   const int nb = n_buckets < tiles ? n_buckets : tiles;
+  v0.clear();
+  v1.clear();
   int t0 = 0;
   for (int b = 0; b < nb; ++b) {
     const int t1 = t0 + (tiles - t0) / (nb - b);
-    v0_.push_back(t0 * ce::kTileM);
-    v1_.push_back(t1 * ce::kTileM < V ? t1 * ce::kTileM : V);
+    v0.push_back(t0 * ce::kTileM);
+    v1.push_back(t1 * ce::kTileM < V ? t1 * ce::kTileM : V);
     t0 = t1;
   }
-  v1_.back() = V;
+  v1.back() = V;
+  return nb;
+}
+
+GradReducer::GradReducer(Comm& comm, float* grad, int V, int D, int n_buckets, DType reduce_dtype, void* staging)
+    : comm_(comm), grad_(grad), V_(V), D_(D), dtype_(reduce_dtype), staging_(staging) {
+  NM_REQUIRE(grad && V > 0 && D > 0, "grad reducer: grad, V, D required");
+  NM_REQUIRE(reduce_dtype == DType::f32 || (reduce_dtype == DType::bf16 && staging),
+             "grad reducer: reduce dtype f32, or bf16 with a staging buffer");
+  grad_bucket_ranges(V, n_buckets, v0_, v1_);
   ready_.resize(v0_.size());
   for (auto& e : ready_) NM_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   NM_CUDA(cudaEventCreateWithFlags(&done_, cudaEventDisableTiming));

@@ -43,6 +43,7 @@ SIGS = {
     "nm_comm_destroy": (I32, [VP]),
     "nm_comm_allreduce_f32": (I32, [VP, VP, I64, VP]),
     "nm_grad_reducer_create": (I32, [VP, VP, I32, I32, I32, I32, VP, VP]),
+    "nm_grad_bucket_ranges": (I32, [I32, I32, VP, VP, VP]),
     "nm_grad_reducer_destroy": (I32, [VP]),
     "nm_grad_reducer_reduce_all": (I32, [VP, VP]),
     "nm_grad_reducer_wait": (I32, [VP, VP]),
