@@ -309,7 +309,10 @@ def main():
     lib.nm_ce_profile_read(prof_ms, prof_n)
     lib.nm_ce_profile_enable(0)
     check_status()
-    loss_value = float((lp.double().sum() * gs.double()).item())
+    lsum = lp.double().sum().reshape(1)
+    if dist:
+        dist.all_reduce(lsum)
+    loss_value = float((lsum * gs.double()).item())         # global weighted mean loss of the last step
 
     # ---------------------------------------------------------------- host-input timing (e2e)
     e2e = None

@@ -277,7 +277,7 @@ void readout(CeImpl impl, Rounding r, const CeShape& s, const ReadoutCall& c, co
   const int64_t T = s.T;
   const int D = s.D;
   if (T == 0) return;
-  ew::rmsnorm_fwd(c.state, c.norm_gain, c.norm_out_ws, c.norm_rstd_ws, T, D, eps, st);
+  ew::rmsnorm_fwd(c.state, c.norm_gain, c.norm_out_ws, c.norm_rstd_ws, T, D, eps, st, r);
   if (c.visible_dims < D) launch_zero_cols(c.norm_out_ws, T, D, c.visible_dims, st);
   const bool need_dy = !base.forward_only && (c.d_state || c.dgain_partial);
   CeArgs a = base;
@@ -298,7 +298,7 @@ void readout(CeImpl impl, Rounding r, const CeShape& s, const ReadoutCall& c, co
     dxo = static_cast<bf16_t*>(w.store);
   }
   ew::rmsnorm_bwd_add(c.norm_out_ws, c.state, c.norm_gain, c.norm_rstd_ws, c.d_state, dxo, c.dgain_partial, T, D, eps,
-                      st);
+                      st, r);
 }
 
 }  // namespace ce
