@@ -54,8 +54,8 @@ def build(force=False, verbose=False):
             cmd += ["-Xptxas", "-v"] if verbose else []
         else:
             cmd = [NVCC] + ARCH + COMMON + ["-DNM_BUILD_ID=\"%s\"" % build_id]
-        cmd += ["-c", os.path.join(CSRC, src), "-o", obj]
-        r = subprocess.run(cmd, capture_output=True, text=True)
+        cmd += ["-c", src, "-o", obj]           # relative source name: __FILE__ in messages is the bare file name
+        r = subprocess.run(cmd, capture_output=True, text=True, cwd=CSRC)
         if r.returncode != 0:
             raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))
         if verbose:

@@ -7,8 +7,9 @@
 // ce_sm90.cu:364-495), k_ce_dgrad / k_ce_wgrad / k_ce_gemm_sm90 (ce_gemm.cu:38-392, ce_sm90.cu:558-764) and its
 // cuBLASLt plans (ce_lt.cpp:47-219).
 //
-// One CTA per SM, 192 threads: warp 0 issues the TMA loads (one elected lane), warp 1 allocates TMEM and issues the
-// UMMAs (one elected lane), warps 2-5 are the epilogue (thread = accumulator row = TMEM lane). Tiles are 128 x 256
+// One CTA per SM, 320 threads: warp 0 issues the TMA loads (one elected lane), warp 1 allocates TMEM and issues the
+// UMMAs (one elected lane), warps 2-9 are the epilogue (thread = accumulator row = TMEM lane; two warps per lane
+// quadrant, one for each 128-column half of the tile, so every scheduler has two epilogue warps to alternate between). Tiles are 128 x 256
 // (M x N) with K blocks of 64 bf16 (one 128-byte swizzle row); operands arrive by TMA into a 4-stage ring of
 // SWIZZLE_128B tiles; the f32 accumulator lives in TMEM, two buffers of 256 columns, so the epilogue of tile i runs
 // while the UMMAs of tile i + 1 are issued. TMEM loads are software-pipelined (the next 32 columns load while the
@@ -38,12 +39,17 @@ constexpr int kBBytes = BN * BK * 2;            // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;  // 48 KiB
 constexpr int kBoxBytesMN = 64 * BK * 2;        // one MN-major box: 64 k-rows of 128 bytes = 8 KiB
 constexpr int kTmemCols = 512;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 enum Epi : int { kEpiLogits = 0, kEpiDx = 1, kEpiDw = 2, kEpiTest = 3 };
 
-// epilogue staging: 4 warps x 2 buffers x (32 rows x 128 bytes), only for the epilogues that leave through TMA
+// epilogue staging: one 32-row x 128-byte tile per epilogue warp, only for the epilogues that leave through TMA; the
+// logits epilogue adds 1 KiB where the two column halves of a row meet to merge their (max, sum exp)
 constexpr int kEpiBufBytes = 32 * 128;
-__host__ __device__ constexpr int epi_stage_bytes(int epi) { return (epi == kEpiLogits || epi == kEpiDw) ? 4 * 2 * kEpiBufBytes : 0; }
+constexpr int kMergeBytes = BM * 8;
+__host__ __device__ constexpr int epi_stage_bytes(int epi) {
+  return (epi == kEpiLogits || epi == kEpiDw) ? kEpiWarps * kEpiBufBytes + (epi == kEpiLogits ? kMergeBytes : 0) : 0;
+}
 constexpr int smem_bytes(int epi) {
   return kStages * kStageBytes + epi_stage_bytes(epi) + 1024 /*alignment slack*/ + 256 /*barriers*/;
 }
@@ -102,19 +108,39 @@ __device__ __forceinline__ void epi_logits_chunk(const GemmParams& p, float* v, 
   }
   // online (max, sum exp): one rescale of the running sum per 32 columns
   constexpr float kLog2e = 1.4426950408889634f;
-  float cm = -INFINITY;
+  float m_new, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, neg;
+  if (ncols == 32) {                       // every chunk but the last of a ragged vocabulary: no column predicates
+    float c0 = fmaxf(v[0], v[1]), c1 = fmaxf(v[2], v[3]), c2 = fmaxf(v[4], v[5]), c3 = fmaxf(v[6], v[7]);
 #pragma unroll
-  for (int j = 0; j < 32; ++j)
-    if (j < ncols) cm = fmaxf(cm, v[j]);
-  const float m_new = fmaxf(st.m, cm);
-  const float neg = -m_new * kLog2e;
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    for (int j = 8; j < 32; j += 8) {
+      c0 = fmaxf(c0, fmaxf(v[j], v[j + 1]));
+      c1 = fmaxf(c1, fmaxf(v[j + 2], v[j + 3]));
+      c2 = fmaxf(c2, fmaxf(v[j + 4], v[j + 5]));
+      c3 = fmaxf(c3, fmaxf(v[j + 6], v[j + 7]));
+    }
+    m_new = fmaxf(st.m, fmaxf(fmaxf(c0, c1), fmaxf(c2, c3)));
+    neg = -m_new * kLog2e;
 #pragma unroll
-  for (int j = 0; j < 32; j += 4) {
-    a0 += (j < ncols) ? ex2_approx(fmaf(v[j], kLog2e, neg)) : 0.f;
-    a1 += (j + 1 < ncols) ? ex2_approx(fmaf(v[j + 1], kLog2e, neg)) : 0.f;
-    a2 += (j + 2 < ncols) ? ex2_approx(fmaf(v[j + 2], kLog2e, neg)) : 0.f;
-    a3 += (j + 3 < ncols) ? ex2_approx(fmaf(v[j + 3], kLog2e, neg)) : 0.f;
+    for (int j = 0; j < 32; j += 4) {
+      a0 += ex2_approx(fmaf(v[j], kLog2e, neg));
+      a1 += ex2_approx(fmaf(v[j + 1], kLog2e, neg));
+      a2 += ex2_approx(fmaf(v[j + 2], kLog2e, neg));
+      a3 += ex2_approx(fmaf(v[j + 3], kLog2e, neg));
+    }
+  } else {
+    float cm = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) cm = fmaxf(cm, v[j]);
+    m_new = fmaxf(st.m, cm);
+    neg = -m_new * kLog2e;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      a0 += (j < ncols) ? ex2_approx(fmaf(v[j], kLog2e, neg)) : 0.f;
+      a1 += (j + 1 < ncols) ? ex2_approx(fmaf(v[j + 1], kLog2e, neg)) : 0.f;
+      a2 += (j + 2 < ncols) ? ex2_approx(fmaf(v[j + 2], kLog2e, neg)) : 0.f;
+      a3 += (j + 3 < ncols) ? ex2_approx(fmaf(v[j + 3], kLog2e, neg)) : 0.f;
+    }
   }
   // st.m == -inf on the first chunk: ex2(-inf) = 0 and st.s = 0
   st.s = st.s * ex2_approx(fmaf(st.m, kLog2e, neg)) + ((a0 + a1) + (a2 + a3));
@@ -176,15 +202,15 @@ __device__ __forceinline__ void epi_dx_chunk(const GemmParams& p, const float* v
   }
 }
 
-// Staging writers: this lane's row of a 32-row x 128-byte tile, 16-byte pieces XOR-swizzled with the row as
-// SWIZZLE_128B expects (piece j of row r at r * 128 + ((j ^ (r & 7)) << 4); the tile is 1024-byte aligned).
-__device__ __forceinline__ void stage_bf16_half(uint32_t buf, int lane, int half, const float* v) {
+// Staging writers: this lane's row of a 32-row staging tile, 16-byte pieces XOR-swizzled with the row the way the
+// tensor map's swizzle mode expects (the tile is 1024-byte aligned). f32: a 32-row x 128-byte tile (32 columns),
+// SWIZZLE_128B: piece j of row r at r * 128 + ((j ^ (r & 7)) << 4).
+// bf16: a 32-row x 64-byte tile (32 columns), SWIZZLE_64B: piece j of row r at r * 64 + ((j ^ ((r >> 1) & 3)) << 4).
+__device__ __forceinline__ void stage_bf16_chunk(uint32_t buf, int lane, const float* v) {
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    const int j = half * 4 + q;
-    st_shared_v4(buf + lane * 128 + ((j ^ (lane & 7)) << 4), pack2(v[8 * q], v[8 * q + 1]),
-                 pack2(v[8 * q + 2], v[8 * q + 3]), pack2(v[8 * q + 4], v[8 * q + 5]), pack2(v[8 * q + 6], v[8 * q + 7]));
-  }
+  for (int j = 0; j < 4; ++j)
+    st_shared_v4(buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4), pack2(v[8 * j], v[8 * j + 1]),
+                 pack2(v[8 * j + 2], v[8 * j + 3]), pack2(v[8 * j + 4], v[8 * j + 5]), pack2(v[8 * j + 6], v[8 * j + 7]));
 }
 __device__ __forceinline__ void stage_f32_row(uint32_t buf, int lane, const float* v, float scale, bool round_bf16) {
 #pragma unroll
@@ -201,7 +227,7 @@ template <int EPI, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
           const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;            // SWIZZLE_128B tiles need 1024-byte alignment
   uint8_t* smem = smem_raw + (base - raw);
@@ -213,13 +239,16 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
   auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages + 2 + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  auto mfull_bar = [&](int q) { return bar0 + 8u * (2 * kStages + 4 + q); };    // right half's (max, sum) written
+  auto mempty_bar = [&](int q) { return bar0 + 8u * (2 * kStages + 8 + q); };   // left half has read them
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), kEpiWarps); }
+    for (int q = 0; q < 4; ++q) { mbar_init(mfull_bar(q), 1); mbar_init(mempty_bar(q), 1); }
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tmap(&tmA);
@@ -252,7 +281,7 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         decode(tile, mi, ni);
         const int m0 = p.m_off + mi * BM, n0 = ni * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kErrProducerWait)) { ok = false; break; }
+          if (!mbar_wait<true>(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kErrProducerWait)) { ok = false; break; }
           mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
           const uint32_t a_dst = sA + stage * kABytes, b_dst = sB + stage * kBBytes;
           if constexpr (A_MN) {
@@ -305,14 +334,18 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       }
     }
   } else {
-    // -------------------------------------------------------------------- epilogue (warps 2-5)
+    // -------------------------------------------------------------------- epilogue (warps 2-9)
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;          // which 128 columns of the 256-column tile this warp handles
     const int r_local = quad * 32 + lane;
-    const uint32_t stg = sEpi + uint32_t(warp - 2) * 2 * kEpiBufBytes;   // this warp's two staging tiles
-    uint32_t n_bulk = 0;                        // bulk groups this warp has issued (staging tile = n_bulk & 1)
+    const uint32_t stg = sEpi + uint32_t(warp - 2) * kEpiBufBytes;       // this warp's staging tile(s)
+    uint32_t n_bulk = 0;                        // TMA stores this warp has issued (logits: staging half = n_bulk & 1)
+    float2* merge = reinterpret_cast<float2*>(smem + kStages * kStageBytes + kEpiWarps * kEpiBufBytes);
     float scale = 1.f;
     if constexpr (EPI == kEpiDx || EPI == kEpiDw) scale = p.scale ? __ldg(p.scale) : 1.f;
     const bool staged_store = EPI == kEpiLogits && p.store != nullptr && !p.store_f32;
+    const uint64_t store_policy = l2_policy_evict_first();   // the logits store is not read again by this kernel
+    constexpr int kChunks = BN / 32 / 2;       // 32-column chunks per warp
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int b = it & 1;
@@ -322,52 +355,47 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       const int grow = m0 + r_local;
       const bool row_ok = grow < p.M;
       const bool warp_rows_ok = m0 + quad * 32 < p.M;          // any row of this warp inside the matrix
-      if (!mbar_wait(tfull_bar(b), (it >> 1) & 1u, abort_flag, p.status, kErrEpilogueWait)) break;
+      if (!mbar_wait<true>(tfull_bar(b), (it >> 1) & 1u, abort_flag, p.status, kErrEpilogueWait)) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(b * BN);
+      const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(b * BN + half * (BN / 2));
       LogitsRowState st{-INFINITY, 0.f, 0.f, false};
       int tg = -1;
       if constexpr (EPI == kEpiLogits) tg = row_ok ? __ldg(p.targets + grow) : -1;
 
-      // one 32-column chunk held in v[]
+      // one 32-column chunk held in v[]; c counts the chunks of the whole tile (0 .. 7)
       auto process = [&](float* v, int c) {
         const int col0 = n0 + c * 32;
-        if (col0 >= p.N) return;               // uniform over the CTA
+        if (col0 >= p.N) return;               // uniform over the warp
         if constexpr (EPI == kEpiLogits) {
           epi_logits_chunk(p, v, grow, row_ok, col0, tg, st);
           if (staged_store && warp_rows_ok) {
-            // two chunks fill one 64-column staging tile; the tile's previous TMA store must have read it
-            const uint32_t buf = stg + (n_bulk & 1u) * kEpiBufBytes;
-            if ((c & 1) == 0) {
-              if (lane == 0) bulk_wait_read<1>();
-              __syncwarp();
+            // one 32-column staging tile per chunk, two tiles per warp used alternately: the TMA store that last read
+            // the tile about to be written must have finished reading it
+            const uint32_t buf = stg + (n_bulk & 1u) * (kEpiBufBytes / 2);
+            if (lane == 0) bulk_wait_read<1>();
+            __syncwarp();
+            stage_bf16_chunk(buf, lane, v);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {                   // rows and columns beyond the matrix are clipped by the tensor map
+              tma_store_2d_hint(&tmC, buf, col0, m0 + quad * 32, store_policy);
+              bulk_commit();
             }
-            stage_bf16_half(buf, lane, c & 1, v);
-            if ((c & 1) == 1 || col0 + 32 >= p.N) {
-              fence_proxy_async_smem();
-              __syncwarp();
-              if (lane == 0) {                 // rows and columns beyond the matrix are clipped by the tensor map
-                tma_store_2d(&tmC, buf, n0 + (c >> 1) * 64, m0 + quad * 32);
-                bulk_commit();
-              }
-              ++n_bulk;
-            }
+            ++n_bulk;
           }
         } else if constexpr (EPI == kEpiDx) {
           if (row_ok) epi_dx_chunk(p, v, grow, col0, scale);
         } else if constexpr (EPI == kEpiDw) {
           if (warp_rows_ok) {
-            const uint32_t buf = stg + (n_bulk & 1u) * kEpiBufBytes;
-            if (lane == 0) bulk_wait_read<1>();
+            if (lane == 0) bulk_wait_read<0>();
             __syncwarp();
-            stage_f32_row(buf, lane, v, scale, p.round_bf16 != 0);
+            stage_f32_row(stg, lane, v, scale, p.round_bf16 != 0);
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {                   // rows beyond the vocabulary are clipped by the tensor map
-              tma_reduce_add_2d(&tmC, buf, col0, p.m_off + m0 + quad * 32);
+              tma_reduce_add_2d(&tmC, stg, col0, p.m_off + m0 + quad * 32);
               bulk_commit();
             }
-            ++n_bulk;
           }
         } else {
           if (row_ok) {
@@ -379,32 +407,50 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         }
       };
 
-      // software pipeline over the 8 chunks: the next chunk's TMEM load is in flight while this one is processed
+      // software pipeline over this warp's chunks: the next chunk's TMEM load is in flight while one is processed
       float va[32], vb[32];
       __syncwarp();
       tmem_ld32(taddr, va);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; c += 2) {
+      for (int c = 0; c < kChunks; c += 2) {
         tmem_ld_wait(va);
         __syncwarp();
         tmem_ld32(taddr + uint32_t((c + 1) * 32), vb);
-        process(va, c);
+        process(va, half * kChunks + c);
         tmem_ld_wait(vb);
-        if (c + 2 < BN / 32) {
+        if (c + 2 < kChunks) {
           __syncwarp();
           tmem_ld32(taddr + uint32_t((c + 2) * 32), va);
         }
-        process(vb, c + 1);
+        process(vb, half * kChunks + c + 1);
       }
       // the accumulator buffer may be overwritten by the UMMAs of the tile after next
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(b));
       if constexpr (EPI == kEpiLogits) {
-        if (row_ok) {
-          p.tmax[int64_t(ni) * p.ldT + grow] = st.m;
-          p.tsum[int64_t(ni) * p.ldT + grow] = st.s;
-          if (st.hit) p.zt[grow] = st.zt;
+        // the two halves of a row meet in shared memory; the left half merges (left, then right: a fixed order) and
+        // writes the tile's partial. Hand-over by two mbarriers per quadrant, waited on with the bounded wait.
+        if (st.hit) p.zt[grow] = st.zt;
+        const uint32_t mphase = uint32_t(it) & 1u;
+        if (half == 1) {
+          if (!mbar_wait<true>(mempty_bar(quad), mphase ^ 1u, abort_flag, p.status, kErrEpilogueWait)) break;
+          merge[r_local] = make_float2(st.m, st.s);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(mfull_bar(quad));
+        } else {
+          if (!mbar_wait<true>(mfull_bar(quad), mphase, abort_flag, p.status, kErrEpilogueWait)) break;
+          const float2 o = merge[r_local];
+          __syncwarp();
+          if (lane == 0) mbar_arrive(mempty_bar(quad));
+          constexpr float kLog2e = 1.4426950408889634f;
+          const float m = fmaxf(st.m, o.x);      // st.m is finite: the left half always holds at least one valid column
+          const float neg = -m * kLog2e;
+          const float s = st.s * ex2_approx(fmaf(st.m, kLog2e, neg)) + o.y * ex2_approx(fmaf(o.x, kLog2e, neg));
+          if (row_ok) {
+            p.tmax[int64_t(ni) * p.ldT + grow] = m;
+            p.tsum[int64_t(ni) * p.ldT + grow] = s;
+          }
         }
       }
     }
@@ -450,7 +496,7 @@ EncodeFn encode_fn() {
 
 // bf16 matrix with `inner` contiguous elements per row, `outer` rows, row pitch ld elements; box = (box_inner, box_outer)
 CUtensorMap make_tmap(const void* base, uint64_t inner, uint64_t outer, int64_t ld, uint32_t box_inner,
-                      uint32_t box_outer, bool f32 = false) {
+                      uint32_t box_outer, bool f32 = false, bool swizzle64 = false) {
   const int esz = f32 ? 4 : 2;
   NM_REQUIRE(reinterpret_cast<uintptr_t>(base) % 16 == 0, "fused CE: a TMA operand must be 16-byte aligned");
   NM_REQUIRE((ld * esz) % 16 == 0, "fused CE: a TMA operand's row pitch must be a multiple of 16 bytes");
@@ -461,7 +507,8 @@ CUtensorMap make_tmap(const void* base, uint64_t inner, uint64_t outer, int64_t 
   const cuuint32_t box[2] = {box_inner, box_outer};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = encode_fn()(&m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     throw DeviceError("fused CE: cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(r)) + " (inner " +
@@ -476,9 +523,10 @@ CUtensorMap tmap_mnmajor(const void* base, int64_t K, int64_t MN, int64_t ld) {
   return make_tmap(base, uint64_t(MN), uint64_t(K), ld, 64, BK);
 }
 
-// epilogue staging tile as a tensor-map box: 32 rows x 128 bytes (64 bf16 or 32 f32)
+// epilogue staging tile as a tensor-map box: 32 rows x 32 columns (f32: 128-byte rows, SWIZZLE_128B; bf16: 64-byte
+// rows, SWIZZLE_64B)
 CUtensorMap tmap_epilogue(void* base, int64_t rows, int64_t cols, int64_t ld, bool f32) {
-  return make_tmap(base, uint64_t(cols), uint64_t(rows), ld, f32 ? 32 : 64, 32, f32);
+  return make_tmap(base, uint64_t(cols), uint64_t(rows), ld, 32, 32, f32, !f32);
 }
 
 template <int EPI, bool A_MN, bool B_MN>

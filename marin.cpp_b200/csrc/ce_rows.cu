@@ -24,34 +24,56 @@ __device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v <<
 __device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
 // ------------------------------------------------------------------------------------------------ finalize
-// One thread per row. Tiles are merged in ascending order: M = max_i m_i (0 when not finite), S = sum_i s_i exp(m_i - M),
-// lse = log S + M. loss = lse - z[target] + L lse^2 for a row that counts, else 0. rowb = weight (0 for an ignored
-// target or a forward-only call), rowa = rowb (1 + 2 L lse): the two per-row factors of the normalised gradient.
-__global__ void __launch_bounds__(128) k_ce_finalize_rows(FinalizeArgs p) {
-  const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= p.rows) return;
+// 32 rows per CTA (lane = row), 8 warps: warp w merges the tile partials of segment w of the vocabulary in ascending
+// order (m_w = max_i m_i, s_w = sum_i s_i exp(m_i - m_w)); warp 0 then merges the 8 segments in ascending order:
+// M = max_w m_w (0 when not finite), S = sum_w s_w exp(m_w - M), lse = log S + M. The order depends only on the
+// number of tiles, so lse and the loss do not depend on the chunk size or the launch geometry.
+// loss = lse - z[target] + L lse^2 for a row that counts, else 0. rowb = weight (0 for an ignored target or a
+// forward-only call), rowa = rowb (1 + 2 L lse): the two per-row factors of the normalised gradient.
+constexpr int kFinWarps = 8;
+__global__ void __launch_bounds__(32 * kFinWarps) k_ce_finalize_rows(FinalizeArgs p) {
+  __shared__ float sm[kFinWarps][32], ss[kFinWarps][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int r = blockIdx.x * 32 + lane;
+  const bool on = r < p.rows;
+  const int i0 = int(int64_t(p.NT) * w / kFinWarps), i1 = int(int64_t(p.NT) * (w + 1) / kFinWarps);
+  float m = -INFINITY, s = 0.f;
+  if (on) {
+#pragma unroll 4
+    for (int i = i0; i < i1; ++i) m = fmaxf(m, p.tmax[int64_t(i) * p.ldT + r]);
+    const float mm = isfinite(m) ? m : 0.f;
+#pragma unroll 4
+    for (int i = i0; i < i1; ++i) {
+      const int64_t o = int64_t(i) * p.ldT + r;
+      s = __fadd_rn(s, __fmul_rn(p.tsum[o], expf(__fsub_rn(p.tmax[o], mm))));
+    }
+  }
+  sm[w][lane] = m;
+  ss[w][lane] = s;
+  __syncthreads();
+  if (w != 0 || !on) return;
   float M = -INFINITY;
-#pragma unroll 8
-  for (int i = 0; i < p.NT; ++i) M = fmaxf(M, p.tmax[int64_t(i) * p.ldT + r]);
+#pragma unroll
+  for (int k = 0; k < kFinWarps; ++k) M = fmaxf(M, sm[k][lane]);
   if (!isfinite(M)) M = 0.f;
   float S = 0.f;
-#pragma unroll 8
-  for (int i = 0; i < p.NT; ++i) {
-    const int64_t o = int64_t(i) * p.ldT + r;
-    S = __fadd_rn(S, __fmul_rn(p.tsum[o], expf(__fsub_rn(p.tmax[o], M))));
+#pragma unroll
+  for (int k = 0; k < kFinWarps; ++k) {
+    const float mk = isfinite(sm[k][lane]) ? sm[k][lane] : 0.f;
+    S = __fadd_rn(S, __fmul_rn(ss[k][lane], expf(__fsub_rn(mk, M))));   // an empty segment has s = 0
   }
   const float lse = __fadd_rn(logf(S), M);
   const int tg = p.targets[r];
-  const float w = p.weight[r];
+  const float wt = p.weight[r];
   const bool valid = tg >= 0 && tg < p.V && tg != p.ignore_index;
   float loss = 0.f;
-  if (valid && w != 0.f) {
+  if (valid && wt != 0.f) {
     loss = __fsub_rn(lse, p.zt[r]);
     if (p.z_loss != 0.f) loss = __fadd_rn(loss, __fmul_rn(p.z_loss, __fmul_rn(lse, lse)));
   }
   p.lse[r] = lse;
   p.loss_tok[r] = loss;
-  const float rb = (p.grads && valid) ? w : 0.f;
+  const float rb = (p.grads && valid) ? wt : 0.f;
   p.rowb[r] = rb;
   p.rowa[r] = (p.z_loss != 0.f) ? __fmul_rn(rb, __fmaf_rn(2.f * p.z_loss, lse, 1.f)) : rb;
 }
@@ -202,7 +224,7 @@ int grid_for(int64_t n, int threads) {
 
 void launch_finalize(const FinalizeArgs& a, cudaStream_t st) {
   if (a.rows <= 0) return;
-  k_ce_finalize_rows<<<(a.rows + 127) / 128, 128, 0, st>>>(a);
+  k_ce_finalize_rows<<<(a.rows + 31) / 32, 32 * kFinWarps, 0, st>>>(a);
   NM_CUDA(cudaGetLastError());
 }
 

@@ -42,6 +42,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same test, but the hardware may suspend the thread for up to `ns` nanoseconds while the phase is incomplete:
+// for waits that are long by design (an epilogue warp waiting for a whole tile), so that polling does not take issue
+// slots from the warps that feed the tensor cores.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Error bits a kernel ORs into its status word when a wait runs out (one bit per role).
 constexpr uint32_t kErrProducerWait = 1u, kErrMmaWait = 2u, kErrEpilogueWait = 4u, kErrTmemFreeWait = 8u;
 
@@ -50,14 +67,20 @@ constexpr uint32_t kErrProducerWait = 1u, kErrMmaWait = 2u, kErrEpilogueWait = 4
 // Every role polls the abort flag inside its waits, so one expired wait ends the whole CTA, which then frees its TMEM
 // and returns; the host reads the status word and reports a device error.
 constexpr long long kWaitCycles = 3000000000ll;
+template <bool kSuspend = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status,
                                           uint32_t err) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
+    for (int i = 0; i < 64; ++i) {
+      if constexpr (kSuspend) {
+        if (mbar_try_wait_suspend(bar, parity, 2000u)) return true;
+      } else {
+        if (mbar_try_wait(bar, parity)) return true;
+      }
+    }
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitCycles) {
       *abort_flag = 1;
@@ -81,6 +104,31 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src_smem
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src_smem), "r"(c0), "r"(c1)
                : "memory");
+}
+// The same store with an L2 eviction policy (from l2_policy_evict_first): lines written once and read by a later
+// kernel should not push the operands that are being re-read out of L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void tma_store_2d_hint(const void* tmap, uint32_t src_smem, int c0, int c1, uint64_t pol) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src_smem), "r"(c0), "r"(c1), "l"(pol)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const void* tmap, uint32_t bar, int c0, int c1,
+                                                 uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], "
+      "[%2], %5;"
+      ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "l"(pol)
+      : "memory");
 }
 // 2-D tiled reduction shared -> global: global += shared, element-wise f32 add performed at L2.
 __device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, uint32_t src_smem, int c0, int c1) {
