@@ -21,6 +21,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <mutex>
 #include <string>
 
@@ -59,6 +60,10 @@ struct GemmParams {
   int m_off;                // first A coordinate along M (dW vocabulary range start)
   int num_m, num_n;         // tiles
   int m_inner;              // 1: consecutive tile indices walk M first (logits), 0: N first
+  int m_group;              // m_inner only: M tiles are walked in groups of this many (all N tiles of a group before
+                            // the next group), so that the A rows of a group stay in L2 while B streams past
+  int a_3d, b_3d;           // an MN-major operand whose M / N extent is a multiple of 64 is described by a 3-D tensor
+                            // map (64 contiguous, K, groups of 64): one TMA instruction per stage instead of 2 or 4
   uint32_t* status;
   // logits
   void* store; int64_t ldS; int store_f32;
@@ -267,8 +272,16 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   const int num_tiles = p.num_m * p.num_n;
   const int k_blocks = (p.K + BK - 1) / BK;
   auto decode = [&](int tile, int& mi, int& ni) {
-    if (p.m_inner) { mi = tile % p.num_m; ni = tile / p.num_m; }
-    else { ni = tile % p.num_n; mi = tile / p.num_n; }
+    if (p.m_inner) {
+      const int per_group = p.m_group * p.num_n;
+      const int g = tile / per_group, r = tile - g * per_group;
+      const int gm = min(p.m_group, p.num_m - g * p.m_group);   // the last group may be smaller
+      ni = r / gm;
+      mi = g * p.m_group + (r - ni * gm);
+    } else {
+      ni = tile % p.num_n;
+      mi = tile / p.num_n;
+    }
   };
 
   if (warp == 0) {
@@ -276,27 +289,50 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       // ------------------------------------------------------------------ TMA producer
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
+      // L2 eviction hints, fixed per kernel: the logits kernel re-reads the x rows of a tile group for every
+      // vocabulary tile and the dW kernel re-reads the whole x chunk for every vocabulary tile (keep: evict last)
+      constexpr int kAPol = EPI == kEpiLogits ? 2 : 0;
+      constexpr int kBPol = EPI == kEpiDw ? 2 : 0;
+      const uint64_t pol_last = l2_policy_evict_last();
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int mi, ni;
         decode(tile, mi, ni);
         const int m0 = p.m_off + mi * BM, n0 = ni * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait<true>(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kErrProducerWait)) { ok = false; break; }
-          mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+          const uint32_t bar = full_bar(stage);
+          mbar_arrive_expect_tx(bar, kStageBytes);
           const uint32_t a_dst = sA + stage * kABytes, b_dst = sB + stage * kBBytes;
+          const int k0 = kb * BK;
           if constexpr (A_MN) {
+            if (p.a_3d) {
+              if constexpr (kAPol == 2) tma_load_3d_hint(a_dst, &tmA, bar, 0, k0, m0 >> 6, pol_last);
+              else tma_load_3d(a_dst, &tmA, bar, 0, k0, m0 >> 6);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d(a_dst + j * kBoxBytesMN, &tmA, full_bar(stage), m0 + j * 64, kb * BK);
+              for (int j = 0; j < BM / 64; ++j) {
+                if constexpr (kAPol == 2) tma_load_2d_hint(a_dst + j * kBoxBytesMN, &tmA, bar, m0 + j * 64, k0, pol_last);
+                else tma_load_2d(a_dst + j * kBoxBytesMN, &tmA, bar, m0 + j * 64, k0);
+              }
+            }
           } else {
-            tma_load_2d(a_dst, &tmA, full_bar(stage), kb * BK, m0);
+            if constexpr (kAPol == 2) tma_load_2d_hint(a_dst, &tmA, bar, k0, m0, pol_last);
+            else tma_load_2d(a_dst, &tmA, bar, k0, m0);
           }
           if constexpr (B_MN) {
+            if (p.b_3d) {
+              if constexpr (kBPol == 2) tma_load_3d_hint(b_dst, &tmB, bar, 0, k0, n0 >> 6, pol_last);
+              else tma_load_3d(b_dst, &tmB, bar, 0, k0, n0 >> 6);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(b_dst + j * kBoxBytesMN, &tmB, full_bar(stage), n0 + j * 64, kb * BK);
+              for (int j = 0; j < BN / 64; ++j) {
+                if constexpr (kBPol == 2) tma_load_2d_hint(b_dst + j * kBoxBytesMN, &tmB, bar, n0 + j * 64, k0, pol_last);
+                else tma_load_2d(b_dst + j * kBoxBytesMN, &tmB, bar, n0 + j * 64, k0);
+              }
+            }
           } else {
-            tma_load_2d(b_dst, &tmB, full_bar(stage), kb * BK, n0);
+            if constexpr (kBPol == 2) tma_load_2d_hint(b_dst, &tmB, bar, k0, n0, pol_last);
+            else tma_load_2d(b_dst, &tmB, bar, k0, n0);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -522,6 +558,32 @@ CUtensorMap tmap_kmajor(const void* base, int64_t rows, int64_t K, int64_t ld, i
 CUtensorMap tmap_mnmajor(const void* base, int64_t K, int64_t MN, int64_t ld) {
   return make_tmap(base, uint64_t(MN), uint64_t(K), ld, 64, BK);
 }
+// The same operand when MN % 64 == 0, as a 3-D tensor (64 contiguous, K rows of pitch ld, MN / 64 groups 64 elements
+// apart): a box of (64, 64 k, `groups`) lands in shared memory as `groups` consecutive 64-k x 128-byte blocks, which
+// is the layout the 2-D boxes are placed in one by one.
+CUtensorMap tmap_mnmajor_3d(const void* base, int64_t K, int64_t MN, int64_t ld, int groups) {
+  NM_REQUIRE(MN % 64 == 0, "fused CE: the 3-D operand map needs an extent that is a multiple of 64");
+  NM_REQUIRE(reinterpret_cast<uintptr_t>(base) % 16 == 0 && (ld * 2) % 16 == 0, "fused CE: TMA operand alignment");
+  CUtensorMap m;
+  const cuuint64_t dims[3] = {64, cuuint64_t(K), cuuint64_t(MN / 64)};
+  const cuuint64_t strides[2] = {cuuint64_t(ld) * 2, 128};
+  const cuuint32_t box[3] = {64, BK, cuuint32_t(groups)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw DeviceError("fused CE: cuTensorMapEncodeTiled (3-D) failed with CUresult " + std::to_string(int(r)));
+  return m;
+}
+CUtensorMap tmap_mn_a(const void* base, int64_t K, int64_t MN, int64_t ld, int& is3d) {
+  is3d = MN % 64 == 0;
+  return is3d ? tmap_mnmajor_3d(base, K, MN, ld, BM / 64) : tmap_mnmajor(base, K, MN, ld);
+}
+CUtensorMap tmap_mn_b(const void* base, int64_t K, int64_t MN, int64_t ld, int& is3d) {
+  is3d = MN % 64 == 0;
+  return is3d ? tmap_mnmajor_3d(base, K, MN, ld, BN / 64) : tmap_mnmajor(base, K, MN, ld);
+}
 
 // epilogue staging tile as a tensor-map box: 32 rows x 32 columns (f32: 128-byte rows, SWIZZLE_128B; bf16: 64-byte
 // rows, SWIZZLE_64B)
@@ -549,6 +611,9 @@ void launch_logits(const LogitsArgs& a, cudaStream_t st) {
   GemmParams p{};
   p.M = a.rows; p.N = a.V; p.K = a.D; p.m_off = 0;
   p.num_m = (a.rows + BM - 1) / BM; p.num_n = (a.V + BN - 1) / BN; p.m_inner = 1;
+  // rows are walked in groups whose x tiles (group x 128 x D bf16) take about 16 MiB of L2: x is then read from HBM
+  // once per launch and W once per group, instead of x once per vocabulary tile
+  p.m_group = int(std::max<int64_t>(1, std::min<int64_t>(p.num_m, (int64_t(16) << 20) / (int64_t(BM) * a.D * 2))));
   p.status = a.status;
   p.store = a.store; p.ldS = a.ldS; p.store_f32 = a.store_f32;
   p.tmax = a.tmax; p.tsum = a.tsum; p.ldT = a.ldT; p.zt = a.zt; p.targets = a.targets; p.bias = a.bias;
@@ -564,11 +629,12 @@ void launch_dgrad(const DgradArgs& a, cudaStream_t st) {
   GemmParams p{};
   p.M = a.rows; p.N = a.D; p.K = a.V; p.m_off = 0;
   p.num_m = (a.rows + BM - 1) / BM; p.num_n = (a.D + BN - 1) / BN; p.m_inner = 0;
+  p.m_group = 1;
   p.status = a.status;
   p.scale = a.scale; p.dx_old = a.dx_old; p.dx_out = a.dx_out; p.acc_mode = a.dx_old ? a.acc_mode : 0;
   p.out_f32 = a.out_f32; p.ldo = a.D;
   const CUtensorMap ta = tmap_kmajor(a.n, a.rows, a.V, a.ldn, BM);
-  const CUtensorMap tb = tmap_mnmajor(a.w, a.V, a.D, a.ldw);
+  const CUtensorMap tb = tmap_mn_b(a.w, a.V, a.D, a.ldw, p.b_3d);
   launch<kEpiDx, false, true>(ta, tb, ta, p, st);
 }
 
@@ -579,10 +645,11 @@ void launch_wgrad(const WgradArgs& a, cudaStream_t st) {
   GemmParams p{};
   p.M = a.v1 - a.v0; p.N = a.D; p.K = a.rows; p.m_off = a.v0;
   p.num_m = (p.M + BM - 1) / BM; p.num_n = (a.D + BN - 1) / BN; p.m_inner = 0;
+  p.m_group = 1;
   p.status = a.status;
   p.scale = a.scale; p.dw = a.dw; p.round_bf16 = a.round_bf16;
-  const CUtensorMap ta = tmap_mnmajor(a.n, a.rows, a.V, a.ldn);
-  const CUtensorMap tb = tmap_mnmajor(a.x, a.rows, a.D, a.ldx);
+  const CUtensorMap ta = tmap_mn_a(a.n, a.rows, a.V, a.ldn, p.a_3d);
+  const CUtensorMap tb = tmap_mn_b(a.x, a.rows, a.D, a.ldx, p.b_3d);
   const CUtensorMap tc = tmap_epilogue(a.dw, a.V, a.D, a.D, true);
   launch<kEpiDw, true, true>(ta, tb, tc, p, st);
 }
@@ -593,17 +660,18 @@ void launch_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64
   NM_REQUIRE(M > 0 && N > 0 && K > 0, "test gemm: M, N, K > 0");
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.m_off = 0;
-  p.num_m = (M + BM - 1) / BM; p.num_n = (N + BN - 1) / BN; p.m_inner = 0;
+  p.num_m = (M + BM - 1) / BM; p.num_n = (N + BN - 1) / BN;
+  p.m_inner = kind == 0; p.m_group = 3;          // the grouped walk is exercised by the K-major test
   p.status = status; p.c = c; p.ldc = ldc;
   if (kind == 0) {
     const CUtensorMap ta = tmap_kmajor(a, M, K, lda, BM);
     launch<kEpiTest, false, false>(ta, tmap_kmajor(b, N, K, ldb, BN), ta, p, st);
   } else if (kind == 1) {
     const CUtensorMap ta = tmap_kmajor(a, M, K, lda, BM);
-    launch<kEpiTest, false, true>(ta, tmap_mnmajor(b, K, N, ldb), ta, p, st);
+    launch<kEpiTest, false, true>(ta, tmap_mn_b(b, K, N, ldb, p.b_3d), ta, p, st);
   } else {
-    const CUtensorMap ta = tmap_mnmajor(a, K, M, lda);
-    launch<kEpiTest, true, true>(ta, tmap_mnmajor(b, K, N, ldb), ta, p, st);
+    const CUtensorMap ta = tmap_mn_a(a, K, M, lda, p.a_3d);
+    launch<kEpiTest, true, true>(ta, tmap_mn_b(b, K, N, ldb, p.b_3d), ta, p, st);
   }
 }
 
