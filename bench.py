@@ -398,6 +398,11 @@ def main():
     dom_launch_ms = prof_ms[names.index(dom)] / max(1, prof_n[names.index(dom)])
     dom_flop_launch = 2.0 * R * T * D * V * args.steps / max(1, prof_n[names.index(dom)])
     achieved = dom_flop_launch / (dom_launch_ms * 1e-3) / 1e12
+    # DRAM bytes per launch of each tcgen05 kernel at 16384 rows x 2048 x 128256, from one ncu capture of this bench
+    # (dram__bytes_read.sum + dram__bytes_write.sum; summary under profiles/); unknown for other shapes
+    traffic = None
+    if (D, V, chunk) == (2048, 128256, 16384):
+        traffic = {"logits": 6.40e9, "dw": 10.07e9, "dx": 8.04e9}[dom]
     out = {
         "metric": "fused_ce_fwd_bwd_tokens_per_s", "value": tokens / (ms_total * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -413,7 +418,7 @@ def main():
         "e2e": e2e,
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": "tensor", "kernel": f"k_ce_umma<{dom}>", "achieved": achieved, "peak": pk["sustained"],
-                     "unit": "TFLOP/s", "frac": achieved / pk["sustained"], "traffic": None,
+                     "unit": "TFLOP/s", "frac": achieved / pk["sustained"], "traffic": traffic,
                      "peak_source": f"{pk['source']} (sustained; burst {pk['burst']})",
                      "frac_of_burst": achieved / pk["burst"], "launch_ms": dom_launch_ms,
                      "path_tflops": path_tflops, "path_frac": path_tflops / pk["sustained"],
