@@ -263,13 +263,32 @@ def main():
                                   nmce.ptr(dw), None, 0, 0, T, D, V, chunk, nmce.ptr(ws), sp, float(L), -100,
                                   reducer if last else None)
 
+    if R > 1:   # pls: every layer's readout state goes through the readout entry point (norm + CE + norm backward)
+        gain = torch.ones(D, dtype=torch.bfloat16, device=dev)
+        norm_out = torch.empty_like(X)
+        norm_rstd = torch.empty(T, dtype=torch.float32, device=dev)
+        d_state = torch.zeros_like(X)
+        dgain_part = torch.zeros(int(lib.nm_norm_partial_rows(T)), D, dtype=torch.float32, device=dev)
+
+    def readout(x_in, y_in, wt_in, r):
+        lib.nm_ce_readout(1, 0, 1, nmce.ptr(x_in), nmce.ptr(gain), nmce.ptr(norm_rstd), nmce.ptr(norm_out),
+                          nmce.ptr(W), nmce.ptr(dw), nmce.ptr(dgain_part), nmce.ptr(gs), nmce.ptr(d_state), D,
+                          nmce.ptr(y_in), nmce.ptr(wt_in), nmce.ptr(loss), nmce.ptr(lse), nmce.ptr(lp[r]), 0, T, D, V,
+                          chunk, 1e-5, nmce.ptr(ws), sp)
+
     def step(inputs=None):
-        """zero dW, every readout's fused CE (dW accumulates), the dW all-reduce overlapped with the last dX."""
+        """zero dW, every readout's fused CE (dW accumulates), the dW all-reduce overlapped with the last dX (one
+        readout) or issued once after the last readout (pls)."""
         dw.zero_()
         for r in range(R):
             x_in, y_in, wt_in = inputs if inputs is not None else (Xs[r], Y, WT)
-            ce(x_in, y_in, wt_in, r, last=(r == R - 1))
+            if R > 1:
+                readout(x_in, y_in, wt_in, r)
+            else:
+                ce(x_in, y_in, wt_in, r, last=True)
         if reducer:
+            if R > 1:
+                lib.nm_grad_reducer_reduce_all(reducer, sp)
             lib.nm_grad_reducer_wait(reducer, sp)
 
     def barrier():
@@ -282,8 +301,12 @@ def main():
         lib.nm_ce_device_status(nmce.ptr(ws), sp, ctypes.byref(st))
 
     launches_per_step = R * (n_chunks * 6)                 # logits, finalize, dlogits, dW, dX, chunk loss per chunk
-    if reducer:                                            # the last chunk's dW runs per bucket (+ the bf16 casts)
-        launches_per_step += (args.buckets - 1) + (2 * args.buckets if cfg["reduce"] == "bf16" else 0)
+    if R > 1:
+        launches_per_step += R * 2                         # the readout's RMSNorm forward and backward
+    if reducer and R == 1:                                 # the last chunk's dW runs per bucket
+        launches_per_step += args.buckets - 1
+    if reducer and cfg["reduce"] == "bf16":
+        launches_per_step += 2 * args.buckets              # casts around the bf16 all-reduce
 
     # ---------------------------------------------------------------- device-resident timing (value)
     for _ in range(args.warmup):

@@ -36,14 +36,26 @@ int nm_fused_linear_ce(int impl, int rounding, int io, int logits_store, const v
                        float* dw /*nullable*/, float* dw_microbatch /*nullable*/, int dw_round, int forward_only,
                        int64_t T, int D, int V, int chunk_rows, void* workspace, void* stream);
 
-/* ---- the RMSNorm pair the readout head needs (reference include/marincpp/capi.h:36-39,
- *      src/kernels/elementwise/capi_ew.h:22,36); dtype 1 = bf16 storage only -------------------------------------- */
+/* ---- the step on either side of the fused CE (reference include/marincpp/capi.h:29-31, 36-48): the metadata kernel
+ *      that produces targets and weights, the RMSNorm pair of the readout head, and the sandwich tail whose forward
+ *      produces the CE input (final norm) and whose backward consumes the CE's dX. dtype 1 = bf16 storage only.
+ *      dgain / dg_next / dg_post: f32 [D], overwritten with the fixed-order reduction of the per-part partials,
+ *      rounded to bf16 under levanter rounding; NULL skips it (these entry points make a stream-ordered allocation
+ *      for the partials, as the reference's test entry points do) ------------------------------------------------ */
+int nm_doc_meta(const int32_t* tokens, const uint8_t* row_valid, int rows, int S, int32_t eos, int max_segs,
+                int32_t* targets, float* weight, int32_t* pos, int32_t* cu_seqlens, int32_t* n_segs,
+                int32_t* row_seg_start, uint32_t* overflow, void* stream);
 int nm_rmsnorm_fwd(int dtype, int rounding, const void* x, const void* gain, void* y, float* rstd, int64_t T, int D,
                    float eps, void* stream);
-int64_t nm_norm_partial_rows(int64_t T);
-int nm_rmsnorm_bwd_add_partial(int dtype, int rounding, const void* dy, const void* x, const void* gain,
-                               const float* rstd, const void* dres, void* dx, float* dgain_partial, int64_t T, int D,
-                               float eps, void* stream);
+int nm_rmsnorm_bwd_add(int dtype, int rounding, const void* dy, const void* x, const void* gain, const float* rstd,
+                       const void* dres, void* dx, float* dgain, int64_t T, int D, float eps, void* stream);
+int nm_sandwich_tail_fwd(int dtype, int rounding, const void* branch, const void* x_in, const void* g_post,
+                         const void* g_next, void* x_out, void* a_next, float* rstd_post, float* rstd_next, int64_t T,
+                         int D, float eps, void* stream);
+int nm_sandwich_tail_bwd(int dtype, int rounding, const void* dx_out, const void* da_next, const void* x_out,
+                         const void* g_next, const float* rstd_next, const void* branch, const void* g_post,
+                         const float* rstd_post, void* dx_in, void* dbranch, float* dg_next, float* dg_post,
+                         int64_t T, int D, float eps, void* stream);
 
 #ifdef __cplusplus
 }

@@ -10,6 +10,7 @@
 #include "ew_api.hpp"
 #include "marincpp/capi.h"
 #include "marincpp/capi_ce.h"
+#include "marincpp/capi_ew.h"
 #include "marincpp/comm.hpp"
 
 namespace {
@@ -196,6 +197,74 @@ int nm_rmsnorm_bwd_add_partial(int dtype, int rounding, const void* dy, const vo
     nm::ew::rmsnorm_bwd_add(static_cast<const nm::bf16_t*>(dy), static_cast<const nm::bf16_t*>(x),
                             static_cast<const nm::bf16_t*>(gain), rstd, static_cast<const nm::bf16_t*>(dres),
                             static_cast<nm::bf16_t*>(dx), dgain_partial, T, D, eps, S(stream), rounding_of(rounding));
+  });
+}
+
+int nm_rmsnorm_bwd_add(int dtype, int rounding, const void* dy, const void* x, const void* gain, const float* rstd,
+                       const void* dres, void* dx, float* dgain, int64_t T, int D, float eps, void* stream) {
+  return nm::capi_call([&] {
+    NM_REQUIRE(dtype == 1, "nm_rmsnorm_bwd_add: bf16 storage (dtype 1) only");
+    const nm::Rounding r = rounding_of(rounding);
+    const int64_t rows = nm::ew::norm_partial_rows(T);
+    float* part = nullptr;   // test path, as in the reference: the partial buffer is a stream-ordered allocation
+    if (dgain) NM_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&part), size_t(rows) * D * 4, S(stream)));
+    nm::ew::rmsnorm_bwd_add(static_cast<const nm::bf16_t*>(dy), static_cast<const nm::bf16_t*>(x),
+                            static_cast<const nm::bf16_t*>(gain), rstd, static_cast<const nm::bf16_t*>(dres),
+                            static_cast<nm::bf16_t*>(dx), part, T, D, eps, S(stream), r);
+    if (dgain) {
+      nm::ew::reduce_partials_rows(part, int(rows), D, dgain, false, r == nm::Rounding::Levanter, S(stream));
+      NM_CUDA(cudaFreeAsync(part, S(stream)));
+    }
+  });
+}
+int nm_sandwich_tail_fwd(int dtype, int rounding, const void* branch, const void* x_in, const void* g_post,
+                         const void* g_next, void* x_out, void* a_next, float* rstd_post, float* rstd_next, int64_t T,
+                         int D, float eps, void* stream) {
+  return nm::capi_call([&] {
+    NM_REQUIRE(dtype == 1, "nm_sandwich_tail_fwd: bf16 storage (dtype 1) only");
+    auto B = [](const void* p) { return static_cast<const nm::bf16_t*>(p); };
+    nm::ew::sandwich_tail_fwd(B(branch), B(x_in), B(g_post), B(g_next), static_cast<nm::bf16_t*>(x_out),
+                              static_cast<nm::bf16_t*>(a_next), rstd_post, rstd_next, T, D, eps, S(stream),
+                              rounding_of(rounding));
+  });
+}
+int nm_sandwich_tail_bwd(int dtype, int rounding, const void* dx_out, const void* da_next, const void* x_out,
+                         const void* g_next, const float* rstd_next, const void* branch, const void* g_post,
+                         const float* rstd_post, void* dx_in, void* dbranch, float* dg_next, float* dg_post,
+                         int64_t T, int D, float eps, void* stream) {
+  return nm::capi_call([&] {
+    NM_REQUIRE(dtype == 1, "nm_sandwich_tail_bwd: bf16 storage (dtype 1) only");
+    const nm::Rounding r = rounding_of(rounding);
+    const int64_t rows = nm::ew::norm_partial_rows(T);
+    float* part = nullptr;   // test path: two partial buffers in one stream-ordered allocation
+    NM_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&part), size_t(rows) * D * 4 * 2, S(stream)));
+    float* pn = part;
+    float* pp = part + size_t(rows) * D;
+    auto B = [](const void* p) { return static_cast<const nm::bf16_t*>(p); };
+    nm::ew::sandwich_tail_bwd(B(dx_out), B(da_next), B(x_out), B(g_next), rstd_next, B(branch), B(g_post), rstd_post,
+                              static_cast<nm::bf16_t*>(dx_in), static_cast<nm::bf16_t*>(dbranch), dg_next ? pn : nullptr,
+                              (dg_post && g_post) ? pp : nullptr, T, D, eps, S(stream), r);
+    const bool rbf = r == nm::Rounding::Levanter;
+    if (dg_next) nm::ew::reduce_partials_rows(pn, int(rows), D, dg_next, false, rbf, S(stream));
+    if (dg_post && g_post) nm::ew::reduce_partials_rows(pp, int(rows), D, dg_post, false, rbf, S(stream));
+    NM_CUDA(cudaFreeAsync(part, S(stream)));
+  });
+}
+int nm_doc_meta(const int32_t* tokens, const uint8_t* row_valid, int rows, int S_, int32_t eos, int max_segs,
+                int32_t* targets, float* weight, int32_t* pos, int32_t* cu_seqlens, int32_t* n_segs,
+                int32_t* row_seg_start, uint32_t* overflow, void* stream) {
+  return nm::capi_call([&] {
+    nm::ew::doc_meta(tokens, row_valid, rows, S_, eos, max_segs, targets, weight, pos, cu_seqlens, n_segs,
+                     row_seg_start, overflow, S(stream));
+  });
+}
+int nm_sum_fixed(const float* x, int64_t n, float* out, void* stream) {
+  return nm::capi_call([&] { nm::ew::sum_fixed(x, n, out, S(stream)); });
+}
+int nm_reduce_partials_rows(const float* partial, int n_blocks, int width, float* out, int accumulate, int round_bf16,
+                            void* stream) {
+  return nm::capi_call([&] {
+    nm::ew::reduce_partials_rows(partial, n_blocks, width, out, accumulate != 0, round_bf16 != 0, S(stream));
   });
 }
 

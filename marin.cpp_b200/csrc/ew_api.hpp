@@ -25,4 +25,28 @@ void rmsnorm_bwd_add(const bf16_t* dy, const bf16_t* x, const bf16_t* gain, cons
                      bf16_t* dx, float* dgain_partial, int64_t T, int D, float eps, cudaStream_t st,
                      Rounding r = Rounding::Levanter);
 
+
+// Sandwich tail (ew_sandwich.cu): y = g_post ? norm(branch; g_post) : branch; x_out = bf16(x_in + y);
+// a_next = norm(x_out; g_next) (a_next may be nullptr). Reference elementwise.hpp:101-122.
+void sandwich_tail_fwd(const bf16_t* branch, const bf16_t* x_in, const bf16_t* g_post, const bf16_t* g_next,
+                       bf16_t* x_out, bf16_t* a_next, float* rstd_post, float* rstd_next, int64_t T, int D, float eps,
+                       cudaStream_t st, Rounding r = Rounding::Levanter);
+// dx_mid = dx_out + norm_next_bwd(da_next); dx_in = dx_mid (may alias dx_out); dbranch = norm_post_bwd(dx_mid) or
+// dx_mid; gain partials [norm_partial_rows(T), D] (nullptr: skipped)
+void sandwich_tail_bwd(const bf16_t* dx_out, const bf16_t* da_next, const bf16_t* x_out, const bf16_t* g_next,
+                       const float* rstd_next, const bf16_t* branch, const bf16_t* g_post, const float* rstd_post,
+                       bf16_t* dx_in, bf16_t* dbranch, float* pg_next, float* pg_post, int64_t T, int D, float eps,
+                       cudaStream_t st, Rounding r = Rounding::Levanter);
+
+// Microbatch metadata from token rows [rows, S] (ew_misc.cu): targets (next token; the last position wraps and has
+// weight 0), weight (0 for an invalid row), pos, per-row segment starts [rows, max_segs + 1] (padded with S), packed
+// cu_seqlens [rows * max_segs + 1] (padded with rows * S), the segment count, and an overflow flag set when a row
+// holds more than max_segs segments. Reference elementwise.hpp DocMetaArgs, doc_meta.cu.
+void doc_meta(const int32_t* tokens, const uint8_t* row_valid, int rows, int S, int32_t eos, int max_segs,
+              int32_t* targets, float* weight, int32_t* pos, int32_t* cu_seqlens, int32_t* n_segs,
+              int32_t* row_seg_start, uint32_t* overflow, cudaStream_t st);
+void sum_fixed(const float* x, int64_t n, float* out, cudaStream_t st);     // fixed-order sum (loss slots)
+void reduce_partials_rows(const float* partial, int n_blocks, int width, float* out, bool accumulate, bool round_bf16,
+                          cudaStream_t st);
+
 }  // namespace nm::ew

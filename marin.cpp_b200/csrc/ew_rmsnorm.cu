@@ -8,46 +8,19 @@
 
 #include "ce_internal.hpp"
 #include "ew_api.hpp"
+#include "ew_rows.cuh"
 
 namespace nm::ew {
 namespace {
 
-constexpr int kMaxPieces = 32;   // 16-byte pieces per lane: D <= 32 * 32 * 8 = 8192
-constexpr int kWarps = 8;
-
-__device__ __forceinline__ float rb(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
-  const uint4 q = *reinterpret_cast<const uint4*>(p);
-  const uint32_t u[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    f[2 * e] = __uint_as_float(u[e] << 16);
-    f[2 * e + 1] = __uint_as_float(u[e] & 0xffff0000u);
-  }
-}
-__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
-  uint32_t u[4];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const __nv_bfloat162 v = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
-    u[e] = *reinterpret_cast<const uint32_t*>(&v);
-  }
-  *reinterpret_cast<uint4*>(p) = make_uint4(u[0], u[1], u[2], u[3]);
-}
-
 template <bool LEV>
-__global__ void __launch_bounds__(kWarps * 32) k_rmsnorm_fwd(const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(kRowWarps * 32) k_rmsnorm_fwd(const __nv_bfloat16* __restrict__ x,
                                                              const __nv_bfloat16* __restrict__ gain,
                                                              __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
                                                              int64_t T, int D, float eps) {
   const int lane = threadIdx.x & 31;
   const int pieces = D / 8;
-  for (int64_t row = blockIdx.x * int64_t(kWarps) + (threadIdx.x >> 5); row < T; row += int64_t(gridDim.x) * kWarps) {
+  for (int64_t row = blockIdx.x * int64_t(kRowWarps) + (threadIdx.x >> 5); row < T; row += int64_t(gridDim.x) * kRowWarps) {
     const __nv_bfloat16* xr = x + row * D;
     float ss = 0.f;
     for (int pc = lane; pc < pieces; pc += 32) {
@@ -72,17 +45,17 @@ __global__ void __launch_bounds__(kWarps * 32) k_rmsnorm_fwd(const __nv_bfloat16
   }
 }
 
-// One CTA per part of consecutive rows; warp w takes rows r0 + w, r0 + w + kWarps, ... and keeps its gain-gradient
+// One CTA per part of consecutive rows; warp w takes rows r0 + w, r0 + w + kRowWarps, ... and keeps its gain-gradient
 // contributions in registers; the warps' sums are then added in warp order through shared memory.
 template <bool LEV, int NP>   // NP: 16-byte pieces a lane may own (D <= NP * 256)
-__global__ void __launch_bounds__(kWarps * 32) k_rmsnorm_bwd_add(const __nv_bfloat16* __restrict__ dy,
+__global__ void __launch_bounds__(kRowWarps * 32) k_rmsnorm_bwd_add(const __nv_bfloat16* __restrict__ dy,
                                                                  const __nv_bfloat16* __restrict__ x,
                                                                  const __nv_bfloat16* __restrict__ gain,
                                                                  const float* __restrict__ rstd,
                                                                  const __nv_bfloat16* dres, __nv_bfloat16* dx,
                                                                  float* __restrict__ partial, int64_t T, int D,
                                                                  float eps, int64_t parts) {
-  extern __shared__ float sred[];   // [kWarps, D]
+  extern __shared__ float sred[];   // [kRowWarps, D]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int pieces = D / 8;
   const int my = (pieces - lane + 31) / 32;   // pieces this lane owns
@@ -93,7 +66,7 @@ __global__ void __launch_bounds__(kWarps * 32) k_rmsnorm_bwd_add(const __nv_bflo
     for (int i = 0; i < NP; ++i)
 #pragma unroll
       for (int e = 0; e < 8; ++e) dg[i][e] = 0.f;
-    for (int64_t row = r0 + warp; row < r1; row += kWarps) {
+    for (int64_t row = r0 + warp; row < r1; row += kRowWarps) {
       const int64_t off = row * D;
       float s_xx = 0.f, s_xa = 0.f;
       for (int i = 0; i < my; ++i) {
@@ -147,10 +120,10 @@ __global__ void __launch_bounds__(kWarps * 32) k_rmsnorm_bwd_add(const __nv_bflo
           for (int e = 0; e < 8; ++e) sred[warp * D + c0 + e] = dg[i][e];
         }
       __syncthreads();
-      for (int d = threadIdx.x; d < D; d += kWarps * 32) {
+      for (int d = threadIdx.x; d < D; d += kRowWarps * 32) {
         float s = 0.f;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) s = __fadd_rn(s, sred[w * D + d]);
+        for (int w = 0; w < kRowWarps; ++w) s = __fadd_rn(s, sred[w * D + d]);
         partial[p * D + d] = s;
       }
       __syncthreads();
@@ -169,12 +142,12 @@ void rmsnorm_fwd(const bf16_t* x, const bf16_t* gain, bf16_t* y, float* rstd, in
                  cudaStream_t st, Rounding r) {
   NM_REQUIRE(x && gain && T >= 0 && D > 0 && D % 8 == 0, "rmsnorm_fwd: x, gain, D % 8 == 0");
   if (T == 0) return;
-  const int grid = int(std::min<int64_t>((T + kWarps - 1) / kWarps, int64_t(ce::sm_count()) * 8));
+  const int grid = int(std::min<int64_t>((T + kRowWarps - 1) / kRowWarps, int64_t(ce::sm_count()) * 8));
   auto X = reinterpret_cast<const __nv_bfloat16*>(x);
   auto G = reinterpret_cast<const __nv_bfloat16*>(gain);
   auto Y = reinterpret_cast<__nv_bfloat16*>(y);
-  if (r == Rounding::Levanter) k_rmsnorm_fwd<true><<<grid, kWarps * 32, 0, st>>>(X, G, Y, rstd, T, D, eps);
-  else k_rmsnorm_fwd<false><<<grid, kWarps * 32, 0, st>>>(X, G, Y, rstd, T, D, eps);
+  if (r == Rounding::Levanter) k_rmsnorm_fwd<true><<<grid, kRowWarps * 32, 0, st>>>(X, G, Y, rstd, T, D, eps);
+  else k_rmsnorm_fwd<false><<<grid, kRowWarps * 32, 0, st>>>(X, G, Y, rstd, T, D, eps);
   NM_CUDA(cudaGetLastError());
 }
 
@@ -184,13 +157,13 @@ void rmsnorm_bwd_add(const bf16_t* dy, const bf16_t* x, const bf16_t* gain, cons
   NM_REQUIRE(D <= kMaxPieces * 32 * 8, "rmsnorm_bwd_add: D <= 8192");
   if (T == 0) return;
   const int64_t parts = norm_partial_rows(T);
-  const size_t smem = size_t(kWarps) * D * sizeof(float);
+  const size_t smem = size_t(kRowWarps) * D * sizeof(float);
   const bool lev = r == Rounding::Levanter;
   auto kern = D <= 512    ? (lev ? k_rmsnorm_bwd_add<true, 2> : k_rmsnorm_bwd_add<false, 2>)
               : D <= 2048 ? (lev ? k_rmsnorm_bwd_add<true, 8> : k_rmsnorm_bwd_add<false, 8>)
                           : (lev ? k_rmsnorm_bwd_add<true, kMaxPieces> : k_rmsnorm_bwd_add<false, kMaxPieces>);
   NM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-  kern<<<int(parts), kWarps * 32, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(dy),
+  kern<<<int(parts), kRowWarps * 32, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(dy),
                                               reinterpret_cast<const __nv_bfloat16*>(x),
                                               reinterpret_cast<const __nv_bfloat16*>(gain), rstd,
                                               reinterpret_cast<const __nv_bfloat16*>(dres),

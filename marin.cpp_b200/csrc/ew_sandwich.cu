@@ -1,0 +1,257 @@
+// The sandwich tail around a residual add, forward and backward, in bf16 storage: optional post-norm of the branch
+// output, residual add, and the next pre-norm (for the last layer: the final norm whose output feeds the LM head and
+// whose input gradient is what the fused CE's dX flows into). Semantics follow the reference's
+// src/kernels/elementwise/rmsnorm_kernels.cuh:100-235 (k_sandwich_fwd / k_sandwich_bwd):
+//   forward   y = g_post ? norm(branch; g_post) : branch;  x_out = bf16(x_in + y);  a_next = norm(x_out; g_next)
+//   backward  dx_mid = dx_out + norm_next_bwd(da_next);  dx_in = dx_mid;  dbranch = g_post ? norm_post_bwd(dx_mid) : dx_mid
+// with the levanter rounding points of ew_api.hpp (or f32 chains under accurate rounding). One warp per row.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+
+#include "ce_internal.hpp"
+#include "ew_api.hpp"
+#include "ew_rows.cuh"
+
+namespace nm::ew {
+namespace {
+
+template <bool LEV>
+__global__ void __launch_bounds__(kRowWarps * 32) k_sandwich_fwd(const __nv_bfloat16* __restrict__ branch,
+                                                                 const __nv_bfloat16* __restrict__ x_in,
+                                                                 const __nv_bfloat16* __restrict__ g_post,
+                                                                 const __nv_bfloat16* __restrict__ g_next,
+                                                                 __nv_bfloat16* __restrict__ x_out,
+                                                                 __nv_bfloat16* __restrict__ a_next,
+                                                                 float* __restrict__ rstd_post,
+                                                                 float* __restrict__ rstd_next, int64_t T, int D,
+                                                                 float eps) {
+  const int lane = threadIdx.x & 31;
+  const int pieces = D / 8;
+  for (int64_t row = blockIdx.x * int64_t(kRowWarps) + (threadIdx.x >> 5); row < T;
+       row += int64_t(gridDim.x) * kRowWarps) {
+    const int64_t off = row * D;
+    float r_p = 0.f;
+    if (g_post) {
+      float ss = 0.f;
+      for (int pc = lane; pc < pieces; pc += 32) {
+        float b[8];
+        load8(branch + off + pc * 8, b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(b[e], b[e], ss);
+      }
+      r_p = rsqrtf(__fdiv_rn(warp_sum(ss), float(D)) + eps);
+      if (rstd_post && lane == 0) rstd_post[row] = r_p;
+    }
+    // x_out = round(x_in + y); its sum of squares is taken over the rounded values
+    float sx = 0.f;
+    for (int pc = lane; pc < pieces; pc += 32) {
+      float b[8], xi[8], xo[8];
+      load8(branch + off + pc * 8, b);
+      load8(x_in + off + pc * 8, xi);
+      if (g_post) {
+        float g[8];
+        load8(g_post + pc * 8, g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float y = norm_y<LEV>(g[e], b[e], r_p);
+          xo[e] = rb(LEV ? __fadd_rn(xi[e], rb(y)) : xi[e] + y);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) xo[e] = rb(__fadd_rn(xi[e], b[e]));
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sx = fmaf(xo[e], xo[e], sx);
+      store8(x_out + off + pc * 8, xo);
+    }
+    const float r_n = rsqrtf(__fdiv_rn(warp_sum(sx), float(D)) + eps);
+    if (rstd_next && lane == 0) rstd_next[row] = r_n;
+    if (a_next) {
+      for (int pc = lane; pc < pieces; pc += 32) {   // this lane re-reads the pieces it has just written
+        float xo[8], g[8], o[8];
+        load8(x_out + off + pc * 8, xo);
+        load8(g_next + pc * 8, g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = norm_y<LEV>(g[e], xo[e], r_n);
+        store8(a_next + off + pc * 8, o);
+      }
+    }
+  }
+}
+
+// One CTA per part of consecutive rows (the partition of norm_partial_rows); warp w takes rows r0 + w, r0 + w + 8, ...
+// Gain contributions stay in registers per lane and are added across the warps in warp order at the end.
+template <bool LEV, int NP>
+__global__ void __launch_bounds__(kRowWarps * 32) k_sandwich_bwd(const __nv_bfloat16* dx_out,
+                                                                 const __nv_bfloat16* __restrict__ da_next,
+                                                                 const __nv_bfloat16* __restrict__ x_out,
+                                                                 const __nv_bfloat16* __restrict__ g_next,
+                                                                 const float* __restrict__ rstd_next,
+                                                                 const __nv_bfloat16* __restrict__ branch,
+                                                                 const __nv_bfloat16* __restrict__ g_post,
+                                                                 const float* __restrict__ rstd_post,
+                                                                 __nv_bfloat16* dx_in, __nv_bfloat16* dbranch,
+                                                                 float* __restrict__ pg_next,
+                                                                 float* __restrict__ pg_post, int64_t T, int D,
+                                                                 float eps, int64_t parts) {
+  extern __shared__ float sred[];   // [kRowWarps, D]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pieces = D / 8;
+  const int my = (pieces - lane + 31) / 32;
+  for (int64_t p = blockIdx.x; p < parts; p += gridDim.x) {
+    const int64_t r0 = p * T / parts, r1 = (p + 1) * T / parts;
+    float dgn[NP][8], dgp[NP][8];
+#pragma unroll
+    for (int i = 0; i < NP; ++i)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dgn[i][e] = dgp[i][e] = 0.f;
+    for (int64_t row = r0 + warp; row < r1; row += kRowWarps) {
+      const int64_t off = row * D;
+      float s_xx = 0.f, s_xa = 0.f, s_bb = 0.f;
+      for (int i = 0; i < my; ++i) {
+        const int c0 = (lane + 32 * i) * 8;
+        float xo[8], da[8], g[8];
+        load8(x_out + off + c0, xo);
+        load8(da_next + off + c0, da);
+        load8(g_next + c0, g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          s_xx = fmaf(xo[e], xo[e], s_xx);
+          s_xa = fmaf(xo[e], norm_a<LEV>(g[e], da[e]), s_xa);
+        }
+        if (g_post) {
+          float b[8];
+          load8(branch + off + c0, b);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) s_bb = fmaf(b[e], b[e], s_bb);
+        }
+      }
+      s_xx = warp_sum(s_xx);
+      s_xa = warp_sum(s_xa);
+      const float ms_n = __fdiv_rn(s_xx, float(D));
+      const float r_n = rstd_next ? __ldg(rstd_next + row) : rsqrtf(ms_n + eps);
+      const float c2n = norm_c2(s_xa, r_n, ms_n, eps, D);
+      float s_bap = 0.f;
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        if (i < my) {
+          const int c0 = (lane + 32 * i) * 8;
+          float xo[8], da[8], g[8], dxo[8], dxm[8];
+          load8(x_out + off + c0, xo);
+          load8(da_next + off + c0, da);
+          load8(g_next + c0, g);
+          load8(dx_out + off + c0, dxo);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float a = norm_a<LEV>(g[e], da[e]);
+            const float dxn = norm_dx<LEV>(a, r_n, c2n, xo[e]);
+            dgn[i][e] += norm_gc<LEV>(da[e], xo[e], r_n);
+            dxm[e] = rb(LEV ? __fadd_rn(dxo[e], rb(dxn)) : dxo[e] + dxn);
+          }
+          store8(dx_in + off + c0, dxm);
+          if (g_post) {
+            float b[8], gp[8];
+            load8(branch + off + c0, b);
+            load8(g_post + c0, gp);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s_bap = fmaf(b[e], norm_a<LEV>(gp[e], dxm[e]), s_bap);
+          } else if (dbranch != dx_in) {
+            store8(dbranch + off + c0, dxm);
+          }
+        }
+      }
+      if (g_post) {
+        s_bb = warp_sum(s_bb);
+        s_bap = warp_sum(s_bap);
+        const float ms_p = __fdiv_rn(s_bb, float(D));
+        const float r_p = rstd_post ? __ldg(rstd_post + row) : rsqrtf(ms_p + eps);
+        const float c2p = norm_c2(s_bap, r_p, ms_p, eps, D);
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+          if (i < my) {
+            const int c0 = (lane + 32 * i) * 8;
+            float b[8], gp[8], dxm[8], db[8];
+            load8(branch + off + c0, b);
+            load8(g_post + c0, gp);
+            load8(dx_in + off + c0, dxm);   // this lane's own writes of the pass above
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float ap = norm_a<LEV>(gp[e], dxm[e]);
+              db[e] = norm_dx<LEV>(ap, r_p, c2p, b[e]);
+              dgp[i][e] += norm_gc<LEV>(dxm[e], b[e], r_p);
+            }
+            store8(dbranch + off + c0, db);
+          }
+        }
+      }
+    }
+    // partial rows of the gain gradients: warps added in warp order
+    for (int which = 0; which < 2; ++which) {
+      float* out = which == 0 ? pg_next : pg_post;
+      if (!out || (which == 1 && !g_post)) continue;
+#pragma unroll
+      for (int i = 0; i < NP; ++i)
+        if (i < my) {
+          const int c0 = (lane + 32 * i) * 8;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) sred[warp * D + c0 + e] = which == 0 ? dgn[i][e] : dgp[i][e];
+        }
+      __syncthreads();
+      for (int d = threadIdx.x; d < D; d += kRowWarps * 32) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < kRowWarps; ++w) s = __fadd_rn(s, sred[w * D + d]);
+        out[p * D + d] = s;
+      }
+      __syncthreads();
+    }
+  }
+}
+
+}  // namespace
+
+void sandwich_tail_fwd(const bf16_t* branch, const bf16_t* x_in, const bf16_t* g_post, const bf16_t* g_next,
+                       bf16_t* x_out, bf16_t* a_next, float* rstd_post, float* rstd_next, int64_t T, int D, float eps,
+                       cudaStream_t st, Rounding r) {
+  NM_REQUIRE(branch && x_in && g_next && x_out && T >= 0 && D > 0 && D % 8 == 0,
+             "sandwich_tail_fwd: branch, x_in, g_next, x_out required; D % 8 == 0");
+  if (T == 0) return;
+  const int grid = int(std::min<int64_t>((T + kRowWarps - 1) / kRowWarps, int64_t(ce::sm_count()) * 8));
+  auto B = [](const bf16_t* p) { return reinterpret_cast<const __nv_bfloat16*>(p); };
+  auto M = [](bf16_t* p) { return reinterpret_cast<__nv_bfloat16*>(p); };
+  if (r == Rounding::Levanter)
+    k_sandwich_fwd<true><<<grid, kRowWarps * 32, 0, st>>>(B(branch), B(x_in), B(g_post), B(g_next), M(x_out), M(a_next),
+                                                          rstd_post, rstd_next, T, D, eps);
+  else
+    k_sandwich_fwd<false><<<grid, kRowWarps * 32, 0, st>>>(B(branch), B(x_in), B(g_post), B(g_next), M(x_out),
+                                                           M(a_next), rstd_post, rstd_next, T, D, eps);
+  NM_CUDA(cudaGetLastError());
+}
+
+void sandwich_tail_bwd(const bf16_t* dx_out, const bf16_t* da_next, const bf16_t* x_out, const bf16_t* g_next,
+                       const float* rstd_next, const bf16_t* branch, const bf16_t* g_post, const float* rstd_post,
+                       bf16_t* dx_in, bf16_t* dbranch, float* pg_next, float* pg_post, int64_t T, int D, float eps,
+                       cudaStream_t st, Rounding r) {
+  NM_REQUIRE(dx_out && da_next && x_out && g_next && dx_in && dbranch && T >= 0 && D > 0 && D % 8 == 0,
+             "sandwich_tail_bwd: dx_out, da_next, x_out, g_next, dx_in, dbranch required; D % 8 == 0");
+  NM_REQUIRE(!g_post || branch, "sandwich_tail_bwd: a post-norm needs the branch output");
+  NM_REQUIRE(D <= kMaxPieces * 32 * 8, "sandwich_tail_bwd: D <= 8192");
+  if (T == 0) return;
+  const int64_t parts = norm_partial_rows(T);
+  const size_t smem = size_t(kRowWarps) * D * sizeof(float);
+  const bool lev = r == Rounding::Levanter;
+  auto kern = D <= 512    ? (lev ? k_sandwich_bwd<true, 2> : k_sandwich_bwd<false, 2>)
+              : D <= 2048 ? (lev ? k_sandwich_bwd<true, 8> : k_sandwich_bwd<false, 8>)
+                          : (lev ? k_sandwich_bwd<true, kMaxPieces> : k_sandwich_bwd<false, kMaxPieces>);
+  NM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  auto B = [](const bf16_t* p) { return reinterpret_cast<const __nv_bfloat16*>(p); };
+  auto M = [](bf16_t* p) { return reinterpret_cast<__nv_bfloat16*>(p); };
+  kern<<<int(parts), kRowWarps * 32, smem, st>>>(B(dx_out), B(da_next), B(x_out), B(g_next), rstd_next, B(branch),
+                                                 B(g_post), rstd_post, M(dx_in), M(dbranch), pg_next, pg_post, T, D, eps,
+                                                 parts);
+  NM_CUDA(cudaGetLastError());
+}
+
+}  // namespace nm::ew

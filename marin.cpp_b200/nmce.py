@@ -38,6 +38,12 @@ SIGS = {
     "nm_rmsnorm_fwd": (I32, [I32, I32, VP, VP, VP, VP, I64, I32, F32, VP]),
     "nm_norm_partial_rows": (I64, [I64]),
     "nm_rmsnorm_bwd_add_partial": (I32, [I32, I32, VP, VP, VP, VP, VP, VP, VP, I64, I32, F32, VP]),
+    "nm_rmsnorm_bwd_add": (I32, [I32, I32, VP, VP, VP, VP, VP, VP, VP, I64, I32, F32, VP]),
+    "nm_sandwich_tail_fwd": (I32, [I32, I32, VP, VP, VP, VP, VP, VP, VP, VP, I64, I32, F32, VP]),
+    "nm_sandwich_tail_bwd": (I32, [I32, I32, VP, VP, VP, VP, VP, VP, VP, VP, VP, VP, VP, VP, I64, I32, F32, VP]),
+    "nm_doc_meta": (I32, [VP, VP, I32, I32, I32, I32, VP, VP, VP, VP, VP, VP, VP, VP]),
+    "nm_sum_fixed": (I32, [VP, I64, VP, VP]),
+    "nm_reduce_partials_rows": (I32, [VP, I32, I32, VP, I32, I32, VP]),
     "nm_comm_unique_id": (I32, [VP]),
     "nm_comm_create": (I32, [VP, I32, I32, VP]),
     "nm_comm_destroy": (I32, [VP]),

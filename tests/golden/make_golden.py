@@ -59,6 +59,34 @@ def main():
         want = torch.tensor(1.0, dtype=torch.float32) / torch.tensor(float(B * 4095), dtype=torch.float32)
         out[f"grad_scale_B{B}"] = np.float32(want.item())
     np.savez_compressed(os.path.join(HERE, "ce_golden.npz"), **out)
+
+    # ---- doc_meta: the reference's own numpy reference, tests/s3/test_misc.py:17-36. The test module runs its
+    # harness at import time, so only the source of that one function is taken from the file and executed.
+    import ast
+    src = open(os.path.join(a.ref, "tests", "s3", "test_misc.py")).read()
+    fn = next(n for n in ast.parse(src).body if isinstance(n, ast.FunctionDef) and n.name == "doc_meta_ref")
+    ns = {"np": np}
+    exec(compile(ast.Module(body=[fn], type_ignores=[]), "test_misc.py", "exec"), ns)
+    doc_meta_ref = ns["doc_meta_ref"]
+    EOS = 128001
+    ew = {}
+    rng = np.random.default_rng(0)
+    rows, S, max_segs = 6, 640, 8
+    tok = rng.integers(0, 128000, size=(rows, S)).astype(np.int32)
+    tok[0, 0] = EOS
+    tok[0, S - 1] = EOS
+    tok[1, 100:103] = EOS
+    tok[1, 255] = EOS
+    for p_ in rng.choice(S - 1, 12, replace=False):
+        tok[3, p_] = EOS
+    tok[4, rng.choice(S - 1, 5, replace=False)] = EOS
+    valid = np.ones(rows, bool)
+    valid[5] = False
+    t, w, ps, rss, cu, n, ovf = doc_meta_ref(tok, valid, EOS, max_segs)
+    ew.update(dm_tok=tok, dm_valid=valid, dm_max_segs=np.int32(max_segs), dm_eos=np.int32(EOS), dm_targets=t,
+              dm_weight=w, dm_pos=ps, dm_rss=rss, dm_cu=cu, dm_n=np.int32(n), dm_overflow=np.bool_(ovf))
+    np.savez_compressed(os.path.join(HERE, "ew_golden.npz"), **ew)
+    print("wrote", os.path.join(HERE, "ew_golden.npz"))
     print("wrote", os.path.join(HERE, "ce_golden.npz"), {k: np.asarray(v).shape for k, v in out.items()})
 
 

@@ -32,7 +32,7 @@ def lib():
 def rel(a, b):
     a = a.double().flatten() if torch.is_tensor(a) else torch.from_numpy(np.asarray(a, np.float64)).flatten()
     b = b.double().flatten() if torch.is_tensor(b) else torch.from_numpy(np.asarray(b, np.float64)).flatten()
-    a, b = a.cpu(), b.cpu()
+    a, b = a.detach().cpu(), b.detach().cpu()
     return float((a - b).norm() / b.norm().clamp_min(1e-300))
 
 

@@ -88,3 +88,21 @@ def test_zipf_labels():
     assert y.min() == 0 and y.max() < 128256
     c0, c1 = (y == 0).mean(), (y == 1).mean()
     assert abs(c0 / c1 - 2 ** 1.1) < 0.15
+
+
+def test_doc_meta_oracle_matches_reference_numpy_reference():
+    import os
+    import ew_oracle as E
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ew_golden.npz"))
+    got = E.doc_meta(g["dm_tok"], g["dm_valid"], int(g["dm_eos"]), int(g["dm_max_segs"]))
+    want = (g["dm_targets"], g["dm_weight"], g["dm_pos"], g["dm_rss"], g["dm_cu"], int(g["dm_n"]), bool(g["dm_overflow"]))
+    for name, a, b in zip(("targets", "weight", "pos", "row_seg_start", "cu_seqlens", "n", "overflow"), got, want):
+        assert np.array_equal(np.asarray(a), np.asarray(b)), name
+    assert bool(g["dm_overflow"]) and int(g["dm_n"]) > 6
+
+
+def test_sum_fixed_oracle_is_the_chunk_loss_tree(coracle):
+    import ew_oracle as E
+    x = np.random.default_rng(2).standard_normal(5000).astype(np.float32)
+    assert E.sum_fixed(x) == coracle.chunk_loss(x, np.ones_like(x))
+    assert E.sum_fixed(np.zeros(0, np.float32)) == 0
