@@ -206,6 +206,7 @@ def main():
         reference_arm(args, cfg, rank, world)
         return
 
+    os.environ["NCCL_DEBUG"] = os.environ.get("NM_BENCH_NCCL_DEBUG", "NONE")   # NCCL prints its version banner to stdout at any other level: keep stdout to the one JSON line
     import torch
     import nmce
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -289,7 +290,17 @@ def main():
         if reducer:
             if R > 1:
                 lib.nm_grad_reducer_reduce_all(reducer, sp)
+            if comm_events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(stream)
+                comm_events.append(ev)
             lib.nm_grad_reducer_wait(reducer, sp)
+            if comm_events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(stream)
+                comm_events.append(ev)
+
+    comm_events = None       # pairs of events around the wait for the dW all-reduce (its exposed, non-overlapped part)
 
     def barrier():
         if dist:
@@ -317,12 +328,18 @@ def main():
     barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    comm_events = [] if reducer else None
     e0.record(stream)
     for _ in range(args.steps):
         step()
     e1.record(stream)
     barrier()
     clocks = sampler.stop()
+    exposed_comm_ms = None
+    if comm_events:
+        exposed_comm_ms = sum(comm_events[i].elapsed_time(comm_events[i + 1])
+                              for i in range(0, len(comm_events), 2)) / args.steps
+    comm_events = None
     ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     if dist:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -435,6 +452,7 @@ def main():
                    "chunk_rows": chunk, "readouts": R, "parallelism": f"dp{world} (rows sharded, W replicated)",
                    "dw_allreduce": (f"{cfg['reduce']}, {args.buckets} buckets, overlapped with the last dX" if world > 1
                                     else "none (1 GPU)"),
+                   "exposed_allreduce_ms_per_step_rank0": exposed_comm_ms,
                    "l2": "inputs (x, W, logits store: > 5 GB per step) exceed the 126 MB L2; no flush needed",
                    "loss": loss_value},
         "clocks": clocks,

@@ -16,6 +16,11 @@ typedef struct CUevent_st* cudaEvent_t;
 
 namespace nm {
 
+// SMs the compute kernels leave to NCCL while a bucket reduction may be in flight (and the CTA cap given to NCCL).
+// The tcgen05 kernels are persistent with one CTA per SM and nearly all of its shared memory, so a collective's CTAs
+// cannot share an SM with them: without free SMs the all-reduce would only start when the compute kernel ends.
+inline constexpr int kCommSms = 16;
+
 class Comm {
  public:
   static void unique_id(void* id128_host);                     // rank 0; 128 bytes

@@ -222,6 +222,7 @@ void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, c
       const int64_t ldn = store_f32 ? 2 * w.ldS : w.ldS;   // bf16 elements
       // dW first: every kernel that reads x runs before dX is written (dx may alias x)
       if (dw_target) {
+        int reserve = 0;   // SMs left to the collective once a bucket reduction may be in flight
         auto wgrad = [&](int v0, int v1) {
           if (f32io) {   // x = hi + lo: two accumulating launches over the split copy (hi at column 0, lo at 2 D)
             WgradArgs g{w.store, ldn, wf.xs, int64_t(3) * D, n, D, V, v0, v1, a.grad_scale, dw_target, false, w.status};
@@ -231,6 +232,7 @@ void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, c
             launch_wgrad(g, st);
           } else {
             WgradArgs g{w.store, ldn, x_c, int64_t(D), n, D, V, v0, v1, a.grad_scale, dw_target, strict_dw, w.status};
+            g.sm_reserve = reserve;
             ProfScope ps(3, st);
             launch_wgrad(g, st);
           }
@@ -241,6 +243,7 @@ void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, c
             reducer->range(b, v0, v1);
             wgrad(v0, v1);
             reducer->bucket_ready(b, st);
+            reserve = kCommSms;
           }
         } else {
           wgrad(0, V);
@@ -258,6 +261,7 @@ void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, c
         } else {
           DgradArgs g{w.store, ldn, a.w, int64_t(D), n, D, V, a.grad_scale, a.accumulate_dx ? dx_c : nullptr, dx_c,
                       r == Rounding::Levanter ? 1 : 2, false, w.status};
+          if (reducer && c == n_chunks - 1) g.sm_reserve = kCommSms;   // the bucket reductions run beside this kernel
           launch_dgrad(g, st);
         }
       }

@@ -593,13 +593,14 @@ CUtensorMap tmap_epilogue(void* base, int64_t rows, int64_t cols, int64_t ld, bo
 
 template <int EPI, bool A_MN, bool B_MN>
 void launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
-            cudaStream_t st) {
+            cudaStream_t st, int sm_reserve = 0) {
   auto kernel = k_ce_umma<EPI, A_MN, B_MN>;
   constexpr int kSmem = smem_bytes(EPI);
   static_assert(kSmem <= 232448, "dynamic shared memory beyond the 227 KiB a CTA may use");
   NM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
   const int tiles = p.num_m * p.num_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  const int sms = std::max(1, sm_count() - std::max(0, sm_reserve));
+  const int grid = tiles < sms ? tiles : sms;
   kernel<<<grid, kThreads, kSmem, st>>>(ta, tb, tc, p);
   NM_CUDA(cudaGetLastError());
 }
@@ -635,7 +636,7 @@ void launch_dgrad(const DgradArgs& a, cudaStream_t st) {
   p.out_f32 = a.out_f32; p.ldo = a.D;
   const CUtensorMap ta = tmap_kmajor(a.n, a.rows, a.V, a.ldn, BM);
   const CUtensorMap tb = tmap_mn_b(a.w, a.V, a.D, a.ldw, p.b_3d);
-  launch<kEpiDx, false, true>(ta, tb, ta, p, st);
+  launch<kEpiDx, false, true>(ta, tb, ta, p, st, a.sm_reserve);
 }
 
 void launch_wgrad(const WgradArgs& a, cudaStream_t st) {
@@ -651,7 +652,7 @@ void launch_wgrad(const WgradArgs& a, cudaStream_t st) {
   const CUtensorMap ta = tmap_mn_a(a.n, a.rows, a.V, a.ldn, p.a_3d);
   const CUtensorMap tb = tmap_mn_b(a.x, a.rows, a.D, a.ldx, p.b_3d);
   const CUtensorMap tc = tmap_epilogue(a.dw, a.V, a.D, a.D, true);
-  launch<kEpiDw, true, true>(ta, tb, tc, p, st);
+  launch<kEpiDw, true, true>(ta, tb, tc, p, st, a.sm_reserve);
 }
 
 void launch_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,

@@ -79,6 +79,7 @@ struct DgradArgs {
   const float* scale;               // device scalar (*grad_scale)
   const void* dx_old; void* dx_out; int acc_mode; bool out_f32;
   uint32_t* status;
+  int sm_reserve = 0;               // SMs left free (for a collective running beside this kernel)
 };
 void launch_dgrad(const DgradArgs& a, cudaStream_t st);
 
@@ -89,6 +90,7 @@ struct WgradArgs {
   int v0, v1;                       // vocabulary range of this launch (multiples of 128, or V)
   const float* scale; float* dw; bool round_bf16;
   uint32_t* status;
+  int sm_reserve = 0;               // SMs left free (for a collective running beside this kernel)
 };
 void launch_wgrad(const WgradArgs& a, cudaStream_t st);
 

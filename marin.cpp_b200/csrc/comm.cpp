@@ -18,6 +18,7 @@ namespace {
 struct NcclApi {
   ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;   // optional
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -41,6 +42,8 @@ const NcclApi& nccl() {
     };
     api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
     api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+    api.CommInitRankConfig =
+        reinterpret_cast<decltype(api.CommInitRankConfig)>(dlsym(h, "ncclCommInitRankConfig"));
     api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
     api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
     api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
@@ -73,7 +76,15 @@ Comm::Comm(const void* id128_host, int nranks, int rank) : nranks_(nranks), rank
   ncclUniqueId id;
   std::memcpy(&id, id128_host, sizeof(id));
   ncclComm_t c = nullptr;
-  NM_NCCL(nccl().CommInitRank(&c, nranks, id, rank));
+  if (nccl().CommInitRankConfig) {
+    // the collectives of this communicator run beside the persistent tcgen05 kernels, which leave kCommSms SMs free
+    // while a reduction is in flight: cap NCCL at that many CTAs
+    ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+    cfg.maxCTAs = kCommSms;
+    NM_NCCL(nccl().CommInitRankConfig(&c, nranks, id, rank, &cfg));
+  } else {
+    NM_NCCL(nccl().CommInitRank(&c, nranks, id, rank));
+  }
   comm_ = c;
   NM_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
 }
