@@ -15,6 +15,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libmarincpp_kernels.so")
+ARCHIVE = os.path.join(HERE, "libmarincpp_ce.a")
 SOURCES = ["nm_core.cpp", "ce_api.cpp", "capi_ce.cpp", "comm.cpp", "ce_gemm.cu", "ce_rows.cu", "ew_rmsnorm.cu",
            "ce_static_ws.cu", "ew_sandwich.cu", "ew_misc.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
@@ -43,7 +44,8 @@ def build(force=False, verbose=False):
     os.makedirs(OBJ, exist_ok=True)
     stamp = os.path.join(OBJ, "fingerprint")
     fp = _fingerprint()
-    if not force and os.path.exists(LIB) and os.path.exists(stamp) and open(stamp).read() == fp:
+    if (not force and os.path.exists(LIB) and os.path.exists(ARCHIVE) and os.path.exists(stamp)
+            and open(stamp).read() == fp):
         return LIB
     build_id = "b200-fused-ce-" + fp[:12]
 
@@ -69,8 +71,29 @@ def build(force=False, verbose=False):
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
+    # the same objects as a static archive: what a C++ host (the reference trainer) links for the nm:: API, since the
+    # shared library exports only the C ABI
+    if os.path.exists(ARCHIVE):
+        os.remove(ARCHIVE)
+    r = subprocess.run(["ar", "rcs", ARCHIVE] + objs, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("ar failed:\n%s\n%s" % (r.stdout, r.stderr))
     open(stamp, "w").write(fp)
     return LIB
+
+
+def build_call_site_example(out=None):
+    """Compiles tests/cpp/call_site.cpp (the reference trainer's call site against these headers) and links it with
+    the static archive. Returns the executable's path."""
+    build()
+    out = out or os.path.join(HERE, "call_site_example")
+    cmd = [NVCC] + ARCH + ["-O2", "-std=c++17", "-I", os.path.join(ROOT, "include"),
+                           os.path.join(ROOT, "tests", "cpp", "call_site.cpp"), ARCHIVE, "-o", out, "-cudart", "static",
+                           "-ldl"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("call-site example failed to build:\n%s\n%s" % (r.stdout, r.stderr))
+    return out
 
 
 if __name__ == "__main__":

@@ -373,6 +373,42 @@ def test_full_size_properties(T, D, labels, chunk):
     assert torch.isfinite(dw).all() and torch.isfinite(dx.float()).all()
 
 
+def test_cuda_graph_capture_and_replay():
+    """The call allocates nothing and never synchronises, so it can be captured into a CUDA graph (as the reference
+    trainer captures its whole step, src/train/trainer.cpp:155-163); replays give the bits of the eager call."""
+    from gpu_common import O, grad_scale_dev, lib, nmce, same_bits, to_dev
+    T, D, V, chunk = 2500, 512, 8256, 1024
+    x, w, y, wt = O.make_inputs(T, D, V, seed=31, ignore_frac=0.05)
+    X, W, Y, WT = to_dev(x, w, y, wt)
+    gs = grad_scale_dev(WT)
+    ws = torch.empty(lib().nm_ce_workspace_bytes(1, T, D, V, chunk, 1), dtype=torch.uint8, device="cuda")
+    outs = {}
+    for name in ("eager", "graph"):
+        outs[name] = dict(loss=torch.zeros(T, device="cuda"), lse=torch.zeros(T, device="cuda"),
+                          dx=torch.zeros_like(X), dw=torch.zeros(V, D, device="cuda"),
+                          lp=torch.zeros((T + chunk - 1) // chunk, device="cuda"))
+
+    def call(o, stream):
+        lib().nm_fused_linear_ce_ex(1, 0, 1, 1, nmce.ptr(X), nmce.ptr(W), nmce.ptr(Y), nmce.ptr(WT), nmce.ptr(gs), None,
+                                    nmce.ptr(o["loss"]), nmce.ptr(o["lse"]), nmce.ptr(o["lp"]), nmce.ptr(o["dx"]), 0,
+                                    nmce.ptr(o["dw"]), None, 0, 0, T, D, V, chunk, nmce.ptr(ws),
+                                    ctypes.c_void_p(stream), 1e-4, -100, None)
+
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        call(outs["eager"], s.cuda_stream)      # eager first: one-time set-up happens outside any capture
+    s.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        call(outs["graph"], s.cuda_stream)
+    for _ in range(3):                          # dW accumulates: compare after the same number of adds
+        outs["graph"]["dw"].zero_()
+        g.replay()
+    torch.cuda.synchronize()
+    for k in ("loss", "lse", "dx", "dw", "lp"):
+        assert same_bits(outs["graph"][k], outs["eager"][k]), f"graph replay differs from the eager call: {k}"
+
+
 def test_two_devices_same_bits():
     """The same call on GPU 0 and GPU 1 of one process gives the same bits (reference test_ce.py:553-574)."""
     if torch.cuda.device_count() < 2:
