@@ -60,6 +60,12 @@ int nm_ce_device_status(void* workspace, void* stream, uint32_t* status_host);
 int nm_ce_profile_enable(int max_launches);
 int nm_ce_profile_read(double* ms_host /*[6]*/, int* launches_host /*[6]*/);
 
+/* Exercises the time-out path of the bounded device waits without hanging anything: one small CTA waits on an mbarrier
+ * that nobody completes, with a limit of `limit_cycles` SM clocks (at most 2e6, about a millisecond). The waiting
+ * thread must OR the epilogue-wait bit (4) into *status and raise the CTA's abort flag; a second thread waiting on the
+ * same barrier with a long limit must leave through that flag (*saw_abort = 1). The kernel then returns normally. */
+int nm_ce_test_wait_timeout(uint32_t* status, int64_t limit_cycles, int* saw_abort, void* stream);
+
 /* One of the three tcgen05 contractions alone, for unit tests and ncu (kind 0: C[M,N] f32 = A[M,K] B[N,K]^T, both
  * K-major; 1: C[M,N] f32 = A[M,K] B[K,N], B N-major; 2: C[M,N] f32 = A[K,M]^T B[K,N], both MN-major). bf16 operands,
  * row-major with leading dimensions in elements; `status` is a device uint32 the kernel ORs its wait errors into. */

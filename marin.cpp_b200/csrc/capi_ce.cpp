@@ -168,6 +168,11 @@ int nm_ce_profile_read(double* ms_host, int* launches_host) {
   });
 }
 
+int nm_ce_test_wait_timeout(uint32_t* status, int64_t limit_cycles, int* saw_abort, void* stream) {
+  return nm::capi_call(
+      [&] { nm::ce::launch_wait_timeout_probe(status, static_cast<long long>(limit_cycles), saw_abort, S(stream)); });
+}
+
 int nm_ce_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,
                     int N, int K, uint32_t* status, void* stream) {
   return nm::capi_call([&] {

@@ -507,6 +507,30 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   }
 }
 
+// A wait that nothing satisfies, with a short limit: the bounded wait must give up, record its error bit and raise the
+// CTA's abort flag, which the other threads (polling it as the kernel roles do) observe; the kernel then returns
+// normally and the context stays usable. This is how the time-out path of mbar_wait is exercised on a GPU.
+__global__ void __launch_bounds__(64) k_wait_timeout_probe(uint32_t* status, long long limit_cycles, int* saw_abort) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_word = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait(smem_u32(&bar), 0, abort_flag, status, kErrEpilogueWait, limit_cycles);
+    if (ok) atomicOr(status, 0x80000000u);                      // cannot happen: nobody arrives on the barrier
+  } else if (threadIdx.x == 32) {
+    // a second role, waiting on the same never-completed barrier with a long limit: it must leave through the abort
+    const bool ok = mbar_wait<true>(smem_u32(&bar), 0, abort_flag, status, kErrProducerWait, limit_cycles * 1000);
+    if (!ok && *abort_flag) *saw_abort = 1;
+  }
+  __syncthreads();
+}
+
 // ---------------------------------------------------------------------------------------------- host side
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -653,6 +677,13 @@ void launch_wgrad(const WgradArgs& a, cudaStream_t st) {
   const CUtensorMap tb = tmap_mn_b(a.x, a.rows, a.D, a.ldx, p.b_3d);
   const CUtensorMap tc = tmap_epilogue(a.dw, a.V, a.D, a.D, true);
   launch<kEpiDw, true, true>(ta, tb, tc, p, st, a.sm_reserve);
+}
+
+void launch_wait_timeout_probe(uint32_t* status, long long limit_cycles, int* saw_abort, cudaStream_t st) {
+  NM_REQUIRE(status && saw_abort, "wait probe: status and saw_abort required");
+  NM_REQUIRE(limit_cycles > 0 && limit_cycles <= 2000000, "wait probe: limit of at most 2e6 cycles (about 1 ms)");
+  k_wait_timeout_probe<<<1, 64, 0, st>>>(status, limit_cycles, saw_abort);
+  NM_CUDA(cudaGetLastError());
 }
 
 void launch_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,

@@ -94,6 +94,9 @@ struct WgradArgs {
 };
 void launch_wgrad(const WgradArgs& a, cudaStream_t st);
 
+// unit-test entry: one CTA whose bounded wait runs out after `limit_cycles` (<= 2e6) on a barrier nobody completes
+void launch_wait_timeout_probe(uint32_t* status, long long limit_cycles, int* saw_abort, cudaStream_t st);
+
 // unit-test entry: C f32 [M, N] = A B^T in the three operand layouts (kind 0 K/K, 1 K/MN, 2 MN/MN)
 void launch_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,
                       int N, int K, uint32_t* status, cudaStream_t st);

@@ -69,7 +69,7 @@ constexpr uint32_t kErrProducerWait = 1u, kErrMmaWait = 2u, kErrEpilogueWait = 4
 constexpr long long kWaitCycles = 3000000000ll;
 template <bool kSuspend = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status,
-                                          uint32_t err) {
+                                          uint32_t err, long long limit_cycles = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
@@ -82,7 +82,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       }
     }
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > limit_cycles) {
       *abort_flag = 1;
       if (status) atomicOr(status, err);
       return false;

@@ -305,6 +305,31 @@ def test_argument_errors_on_device():
     assert lib().nm_ce_device_arch() == 100 and lib().nm_device_arch() == 100
 
 
+def test_bounded_wait_times_out_and_reports():
+    """The failure path of the device-side waits, made on purpose in the one safe way: a wait on a barrier that nothing
+    completes, limited to a million clocks. It must end by itself, set its status bit, wake the other waiter through
+    the abort flag, and leave the context usable (the next CE call works and reports a clean status)."""
+    from gpu_common import O, grad_scale_dev, lib, nmce, run_ce, to_dev
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    saw = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib().nm_ce_test_wait_timeout(nmce.ptr(status), 1_000_000, nmce.ptr(saw), None)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 4, f"expected the epilogue-wait bit, got {int(status.item())}"
+    assert int(saw.item()) == 1, "the second waiter did not leave through the abort flag"
+    with pytest.raises(nmce.NmError):            # limits beyond a millisecond are refused
+        lib().nm_ce_test_wait_timeout(nmce.ptr(status), 10**9, nmce.ptr(saw), None)
+    # a status word with a bit set is what nm_ce_device_status turns into NM_ERR_DEVICE
+    fake_ws = torch.zeros(64, dtype=torch.int32, device="cuda")
+    fake_ws[0] = 4
+    st = ctypes.c_uint32(0)
+    with pytest.raises(nmce.NmError) as e:
+        lib().nm_ce_device_status(nmce.ptr(fake_ws), None, ctypes.byref(st))
+    assert e.value.status == 2 and st.value == 4
+    x, w, y, wt = O.make_inputs(300, 64, 500, seed=8)
+    X, W, Y, WT = to_dev(x, w, y, wt)
+    run_ce(X, W, Y, WT, grad_scale_dev(WT), chunk=128)      # the context is still healthy
+
+
 def test_dlogits_entry_point():
     """nm_ce_dlogits alone over a bf16 store: n = g (exp(z_s - lse) - onehot), columns >= V zeroed."""
     from gpu_common import lib, nmce, rel
