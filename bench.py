@@ -13,8 +13,10 @@ W is replicated. Rank 0 prints ONE JSON line:
              against the measured dense bf16 peak (MEASURED_PEAKS.json, sustained figure: the kernel is timed inside a
              long step); path_* are the same for the whole 6 T D V path
   cpu_baseline  the CPU oracle (oracle/ce_ref.c, OpenMP on all host cores) timed on a bounded row sample (N = 1 only)
---impl reference times the reference's CPU-side computation of this path: the reference has no CPU implementation
-(its f32 "reference" is a GPU path), so the arm runs the CPU oracle port on the host cores, a bounded row sample per step.
+--impl reference runs the reference itself: its fused-CE module compiled unmodified for sm_100a (oracle/_ref/, built by
+oracle/Makefile where the reference's sources are present) through its own C ABI on the same configuration, on one GPU.
+The reference has no CPU implementation of this path (its f32 "reference" is a GPU path too); when that library is
+absent the arm falls back to timing the CPU oracle port on the host cores, a bounded row sample per step.
 """
 import argparse
 import ctypes
@@ -149,11 +151,87 @@ def cpu_sample(cfg, seconds=12.0, rows0=32):
     return n / t1, n, c.threads(), t1
 
 
+REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libref_ce.so")
+
+
+def reference_arm_gpu(args, cfg):
+    """The reference's own fused-CE module (compiled unmodified for sm_100a by oracle/Makefile into oracle/_ref/),
+    driven through its C ABI on the full configuration: implementation B1, bf16 store, default backends (cuBLASLt for
+    the plain-dz GEMMs, its portable mma.sync logits kernel), i.e. what its trainer would run on this GPU."""
+    import torch
+    import nmce
+    dll = ctypes.CDLL(REF_LIB)
+    for n in ("nm_ce_workspace_bytes", "nm_fused_linear_ce", "nm_last_error"):
+        f = getattr(dll, n)
+        f.restype, f.argtypes = nmce.SIGS[n]
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    T, D, V = cfg["T"], cfg["D"], cfg["V"]
+    R = cfg["readouts"]
+    chunk = min(args.chunk, T)
+    X, W, Y, WT = make_inputs(torch, cfg, 0, dev)
+    gs = (1.0 / WT.sum()).float().reshape(1) / R
+    dx = torch.empty_like(X)
+    dw = torch.zeros(V, D, dtype=torch.float32, device=dev)
+    loss = torch.empty(T, dtype=torch.float32, device=dev)
+    lse = torch.empty(T, dtype=torch.float32, device=dev)
+    lp = torch.zeros((T + chunk - 1) // chunk, dtype=torch.float32, device=dev)
+    ws = torch.empty(dll.nm_ce_workspace_bytes(1, T, D, V, chunk, 1), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev)
+    sp = ctypes.c_void_p(stream.cuda_stream)
+
+    def step():
+        dw.zero_()
+        for _ in range(R):
+            r = dll.nm_fused_linear_ce(1, 0, 1, 1, nmce.ptr(X), nmce.ptr(W), nmce.ptr(Y), nmce.ptr(WT), nmce.ptr(gs),
+                                       None, nmce.ptr(loss), nmce.ptr(lse), nmce.ptr(lp), nmce.ptr(dx), 0, nmce.ptr(dw),
+                                       None, 0, 0, T, D, V, chunk, nmce.ptr(ws), sp)
+            if r != 0:
+                raise RuntimeError("reference nm_fused_linear_ce: " + dll.nm_last_error().decode())
+    for _ in range(max(1, args.warmup)):
+        step()
+    torch.cuda.synchronize(dev)
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize(dev)
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    val = R * T * args.steps / (ms * 1e-3)
+    sample = ("GPU run, not CPU: the reference has no CPU implementation of this path; this is its own CE module "
+              "(B1, bf16 store, cuBLASLt + mma.sync) built unmodified for sm_100a, full configuration, one GPU")
+    print(json.dumps({
+        "impl": "reference", "metric": "fused_ce_fwd_bwd_tokens_per_s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD[args.config], "tokens_per_gpu": R * T, "hidden": D, "vocab": V,
+                   "chunk_rows": chunk, "note": "rank 0 only: the reference's CE module on one GPU (its trainer's "
+                   "multi-GPU loop is not part of this path)",
+                   "path_tflops": 6.0 * R * T * D * V / (ms / args.steps * 1e-3) / 1e12},
+        "clocks": clocks,
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": 0, "kind": "reference", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
 def reference_arm(args, cfg, rank, world):
-    """The reference arm: the reference has no CPU implementation of this path, so this times the CPU oracle port
-    (oracle/ce_ref.c) on the host cores; each step is a bounded row sample of the configuration."""
+    """The reference arm. When the reference's own CE module has been built (oracle/_ref/libref_ce.so) and a GPU is
+    present, that is what runs (see reference_arm_gpu). Otherwise: the reference has no CPU implementation of this
+    path, so the arm times the CPU oracle port (oracle/ce_ref.c) on the host cores, a bounded row sample per step."""
     if rank != 0:
         return
+    if os.path.exists(REF_LIB):
+        try:
+            import torch
+            if torch.cuda.is_available():
+                reference_arm_gpu(args, cfg)
+                return
+        except (OSError, RuntimeError) as e:   # fall through to the CPU port, saying why
+            sys.stderr.write(f"reference library unusable ({e}); timing the CPU oracle port instead\n")
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import ce_oracle as O
     c = O.COracle()

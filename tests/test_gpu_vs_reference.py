@@ -1,0 +1,112 @@
+"""Parity against the REFERENCE ITSELF: the reference's fused-CE module, compiled unmodified for sm_100a by
+oracle/Makefile (target _ref/libref_ce.so), driven through the same C ABI and the same ctypes harness as this library.
+Its implementation A with f32 io (true-f32 cuBLASLt GEMMs + a row kernel) is what the reference calls its reference
+(include/marincpp/kernels/cross_entropy.hpp:18) and what its kernel tests compare against; its B1 is what it would run
+in training on a B200 (portable mma.sync logits kernel + cuBLASLt). Skipped when the library was not built."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libref_ce.so")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not os.path.exists(REF_LIB):
+        pytest.skip("oracle/_ref/libref_ce.so was not built (make -C oracle _ref/libref_ce.so)")
+    from gpu_common import nmce
+    import ctypes
+    dll = ctypes.CDLL(REF_LIB)
+
+    class RefLib:     # the reference exports a subset of the entry points: bind only those
+        path = REF_LIB
+
+        def __init__(self):
+            self.dll = dll
+            for name in ("nm_last_error", "nm_ce_workspace_bytes", "nm_fused_linear_ce", "nm_ce_grad_scale",
+                         "nm_ce_set_backends"):
+                f = getattr(dll, name)
+                f.restype, f.argtypes = nmce.SIGS[name]
+
+        def __getattr__(self, name):
+            f = getattr(dll, name)
+
+            def call(*a):
+                r = f(*a)
+                if name not in nmce.NO_STATUS and r != 0:
+                    raise nmce.NmError(name, r, dll.nm_last_error().decode())
+                return r
+            return call
+    return RefLib()
+
+
+def _ref_call(ref, impl, X, W, Y, WT, gs, chunk, store=1):
+    from gpu_common import nmce
+    T, D = X.shape
+    V = W.shape[0]
+    dx = torch.empty_like(X)
+    dw = torch.zeros(V, D, dtype=torch.float32, device="cuda")
+    lp = torch.empty((T + chunk - 1) // chunk, dtype=torch.float32, device="cuda")
+    ws = torch.empty(ref.nm_ce_workspace_bytes(nmce.IMPLS[impl], T, D, V, chunk, store), dtype=torch.uint8, device="cuda")
+    loss, lse = nmce.ce_call(ref, impl, X, W, Y, WT, gs, dx=dx, dw=dw, loss_partial=lp, chunk=chunk, store=store, ws=ws,
+                             check=False)
+    torch.cuda.synchronize()
+    return loss, lse, dx, dw, lp
+
+
+@pytest.mark.parametrize("T,D,V,labels", [(2125, 512, 8256, "uniform"), (1500, 2048, 16384, "zipf"),
+                                          (700, 1024, 128256, "uniform")])
+def test_against_the_reference_f32_implementation(ref, T, D, V, labels):
+    """This library (bf16 io) against the reference's implementation A with f32 io on the same (bf16-representable)
+    inputs: the north-star parity statement. Bars: scalar loss 1e-4 relative, per-token 2e-5, dX / dW 3e-3, cos 0.9999."""
+    from gpu_common import GRAD_COS, GRAD_REL, LOSS_REL, LOSS_TOK, O, cos, grad_scale_dev, rel, run_ce, to_dev
+    x, w, y, wt = O.make_inputs(T, D, V, seed=T + V, ignore_frac=0.02, labels=labels)
+    X, W, Y, WT = to_dev(x, w, y, wt)
+    gs = grad_scale_dev(WT)
+    mine = run_ce(X, W, Y, WT, gs, chunk=1024)
+    theirs = _ref_call(ref, "A", X.float(), W.float(), Y, WT, gs, 1024, store=0)
+    on = (WT != 0)
+    dl = float((mine[0] - theirs[0]).abs().max())
+    dlse = float((mine[1] - theirs[1]).abs().max())
+    s_m = float((mine[0].double() * WT).sum())
+    s_t = float((theirs[0].double() * WT).sum())
+    rx, cx = rel(mine[2], theirs[2]), cos(mine[2], theirs[2])
+    rw, cw = rel(mine[3], theirs[3]), cos(mine[3], theirs[3])
+    print(f"[parity] vs reference A/f32 T{T} D{D} V{V}: loss {dl:.2e} lse {dlse:.2e} dX rel {rx:.2e} cos {cx:.7f} "
+          f"dW rel {rw:.2e} cos {cw:.7f}")
+    assert dl <= LOSS_TOK and dlse <= LOSS_TOK
+    assert abs(s_m - s_t) <= LOSS_REL * abs(s_t)
+    assert rx <= GRAD_REL and cx >= GRAD_COS and rw <= GRAD_REL and cw >= GRAD_COS
+    assert bool((mine[0][~on] == 0).all()) and bool((theirs[0][~on] == 0).all())
+
+
+def test_against_the_reference_training_path_and_shared_bits(ref):
+    """The reference's B1 (what its trainer runs) on the same bf16 inputs; and the pieces that are specified to the bit:
+    the grad scale and, given the same per-token losses, the per-chunk loss tree."""
+    from gpu_common import GRAD_COS, GRAD_REL, LOSS_TOK, O, cos, grad_scale_dev, lib, nmce, rel, run_ce, to_dev
+    T, D, V, chunk = 3000, 768, 8256, 1024
+    x, w, y, wt = O.make_inputs(T, D, V, seed=5, ignore_frac=0.05)
+    X, W, Y, WT = to_dev(x, w, y, wt)
+    gs = grad_scale_dev(WT)
+    gs_ref = torch.empty(1, dtype=torch.float32, device="cuda")
+    ref.nm_ce_grad_scale(nmce.ptr(WT), T, 1.0, nmce.ptr(gs_ref), None)
+    torch.cuda.synchronize()
+    assert gs.item() == gs_ref.item(), "grad scale bits differ from the reference's kernel"
+    mine = run_ce(X, W, Y, WT, gs, chunk=chunk)
+    for own in (0, 1):
+        ref.nm_ce_set_backends(own, own, -1)
+        theirs = _ref_call(ref, "B1", X, W, Y, WT, gs, chunk)
+        assert float((mine[0] - theirs[0]).abs().max()) <= LOSS_TOK
+        assert float((mine[1] - theirs[1]).abs().max()) <= LOSS_TOK
+        rx, rw = rel(mine[2], theirs[2]), rel(mine[3], theirs[3])
+        print(f"[parity] vs reference B1 ({'own' if own else 'cuBLASLt'} GEMMs): dX rel {rx:.2e} dW rel {rw:.2e}")
+        # both are bf16-rounded results of the same quantity: each is within 1.7e-3 of the truth
+        assert rx <= 1.5 * GRAD_REL and rw <= 1.5 * GRAD_REL
+        assert cos(mine[2], theirs[2]) >= GRAD_COS and cos(mine[3], theirs[3]) >= GRAD_COS
+    ref.nm_ce_set_backends(0, 0, -1)
+    want = O.chunk_loss_tree(theirs[0].cpu().numpy(), wt, chunk)
+    assert theirs[4].cpu().numpy().tobytes() == want.tobytes(), "the oracle's loss tree is the reference kernel's, to the bit"
