@@ -269,6 +269,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=16384)
     ap.add_argument("--buckets", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (small cases for profiling)")
+    ap.add_argument("--cta-pair", default="", help="three digits (logits, dX, dW): 1 = a CTA pair per tile, e.g. 011")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg")
     args = ap.parse_args()
@@ -293,6 +294,8 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     lib = nmce.Lib()
+    if args.cta_pair:
+        lib.nm_ce_set_cta_pair(*[int(ch) for ch in args.cta_pair])
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -419,8 +422,15 @@ def main():
                               for i in range(0, len(comm_events), 2)) / args.steps
     comm_events = None
     ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    exposed_by_rank = None
     if dist:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        # every rank's wait for the all-reduce: the ranks' GPUs run at different power-capped clocks, and the faster
+        # ones wait here for the slowest one's last bucket (the smallest wait is what the collective itself exposes)
+        ex = torch.tensor([exposed_comm_ms or 0.0], dtype=torch.float64, device=dev)
+        allex = [torch.zeros_like(ex) for _ in range(world)]
+        dist.all_gather(allex, ex)
+        exposed_by_rank = [round(float(t.item()), 3) for t in allex]
     ms_total = float(ms.item())
     prof_ms = (ctypes.c_double * 6)()
     prof_n = (ctypes.c_int * 6)()
@@ -531,6 +541,7 @@ def main():
                    "dw_allreduce": (f"{cfg['reduce']}, {args.buckets} buckets, overlapped with the last dX" if world > 1
                                     else "none (1 GPU)"),
                    "exposed_allreduce_ms_per_step_rank0": exposed_comm_ms,
+                   "allreduce_wait_ms_per_step_by_rank": exposed_by_rank,
                    "l2": "inputs (x, W, logits store: > 5 GB per step) exceed the 126 MB L2; no flush needed",
                    "loss": loss_value},
         "clocks": clocks,

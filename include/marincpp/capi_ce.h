@@ -66,9 +66,16 @@ int nm_ce_profile_read(double* ms_host /*[6]*/, int* launches_host /*[6]*/);
  * same barrier with a long limit must leave through that flag (*saw_abort = 1). The kernel then returns normally. */
 int nm_ce_test_wait_timeout(uint32_t* status, int64_t limit_cycles, int* saw_abort, void* stream);
 
+/* How many CTAs work on one accumulator tile in the logits, dX and dW contractions: 0 = one CTA per 128 x 256 tile,
+ * non-zero = a pair of CTAs on one TPC per 256 x 256 tile (tcgen05 cta_group::2; the B operand is staged once per
+ * pair). Results are bit-identical between the two forms. Process-wide; call it while no CE call is in flight. No
+ * counterpart in the reference (its nm_ce_set_backends chooses between its own kernels and cuBLASLt). */
+int nm_ce_set_cta_pair(int logits, int dgrad, int wgrad);
+
 /* One of the three tcgen05 contractions alone, for unit tests and ncu (kind 0: C[M,N] f32 = A[M,K] B[N,K]^T, both
- * K-major; 1: C[M,N] f32 = A[M,K] B[K,N], B N-major; 2: C[M,N] f32 = A[K,M]^T B[K,N], both MN-major). bf16 operands,
- * row-major with leading dimensions in elements; `status` is a device uint32 the kernel ORs its wait errors into. */
+ * K-major; 1: C[M,N] f32 = A[M,K] B[K,N], B N-major; 2: C[M,N] f32 = A[K,M]^T B[K,N], both MN-major; kind + 4: the same
+ * with CTA pairs). bf16 operands, row-major with leading dimensions in elements; `status` is a device uint32 the
+ * kernel ORs its wait errors into. */
 int nm_ce_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,
                     int N, int K, uint32_t* status, void* stream);
 

@@ -20,6 +20,8 @@ namespace nm {
 // The tcgen05 kernels are persistent with one CTA per SM and nearly all of its shared memory, so a collective's CTAs
 // cannot share an SM with them: without free SMs the all-reduce would only start when the compute kernel ends.
 inline constexpr int kCommSms = 16;
+// The value in effect: kCommSms, or the environment variable NM_COMM_SMS (4 .. 64) read once per process.
+int comm_sms();
 
 class Comm {
  public:

@@ -173,6 +173,10 @@ int nm_ce_test_wait_timeout(uint32_t* status, int64_t limit_cycles, int* saw_abo
       [&] { nm::ce::launch_wait_timeout_probe(status, static_cast<long long>(limit_cycles), saw_abort, S(stream)); });
 }
 
+int nm_ce_set_cta_pair(int logits, int dgrad, int wgrad) {
+  return nm::capi_call([&] { nm::ce::set_cta_pair(logits, dgrad, wgrad); });
+}
+
 int nm_ce_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,
                     int N, int K, uint32_t* status, void* stream) {
   return nm::capi_call([&] {

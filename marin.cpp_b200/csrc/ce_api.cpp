@@ -243,7 +243,7 @@ void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, c
             reducer->range(b, v0, v1);
             wgrad(v0, v1);
             reducer->bucket_ready(b, st);
-            reserve = kCommSms;
+            reserve = comm_sms();
           }
         } else {
           wgrad(0, V);
@@ -261,7 +261,7 @@ void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, c
         } else {
           DgradArgs g{w.store, ldn, a.w, int64_t(D), n, D, V, a.grad_scale, a.accumulate_dx ? dx_c : nullptr, dx_c,
                       r == Rounding::Levanter ? 1 : 2, false, w.status};
-          if (reducer && c == n_chunks - 1) g.sm_reserve = kCommSms;   // the bucket reductions run beside this kernel
+          if (reducer && c == n_chunks - 1) g.sm_reserve = comm_sms();   // the bucket reductions run beside this kernel
           launch_dgrad(g, st);
         }
       }

@@ -24,6 +24,7 @@
 #include <algorithm>
 #include <mutex>
 #include <string>
+#include <type_traits>
 
 #include "ce_internal.hpp"
 #include "ptx.cuh"
@@ -34,10 +35,14 @@ namespace {
 using namespace nm::ptx;
 
 constexpr int BM = 128, BN = 256, BK = 64, UK = 16;
-constexpr int kStages = 4;
+// NCTA = 1: one CTA per tile of 128 x 256. NCTA = 2: a pair of CTAs (a cluster of two on one TPC) per tile of
+// 256 x 256; each CTA stages its own 128 rows of A and its own 128 columns of B, the leader issues one UMMA of M = 256
+// over both CTAs' shared memory, and each CTA keeps the accumulator of its own 128 rows in its own TMEM: the B
+// operand crosses L2 -> shared memory once per pair instead of once per CTA.
 constexpr int kABytes = BM * BK * 2;            // 16 KiB
-constexpr int kBBytes = BN * BK * 2;            // 32 KiB
-constexpr int kStageBytes = kABytes + kBBytes;  // 48 KiB
+__host__ __device__ constexpr int b_bytes(int ncta) { return BN / ncta * BK * 2; }                 // 32 / 16 KiB
+__host__ __device__ constexpr int stage_bytes(int ncta) { return kABytes + b_bytes(ncta); }        // 48 / 32 KiB
+__host__ __device__ constexpr int num_stages(int ncta) { return ncta == 2 ? 6 : 4; }
 constexpr int kBoxBytesMN = 64 * BK * 2;        // one MN-major box: 64 k-rows of 128 bytes = 8 KiB
 constexpr int kTmemCols = 512;
 constexpr int kEpiWarps = 8;
@@ -51,14 +56,14 @@ constexpr int kMergeBytes = BM * 8;
 __host__ __device__ constexpr int epi_stage_bytes(int epi) {
   return (epi == kEpiLogits || epi == kEpiDw) ? kEpiWarps * kEpiBufBytes + (epi == kEpiLogits ? kMergeBytes : 0) : 0;
 }
-constexpr int smem_bytes(int epi) {
-  return kStages * kStageBytes + epi_stage_bytes(epi) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int smem_bytes(int epi, int ncta) {
+  return num_stages(ncta) * stage_bytes(ncta) + epi_stage_bytes(epi) + 1024 /*alignment slack*/ + 256 /*barriers*/;
 }
 
 struct GemmParams {
   int M, N, K;              // extents of this launch: accumulator rows, columns, contraction length
   int m_off;                // first A coordinate along M (dW vocabulary range start)
-  int num_m, num_n;         // tiles
+  int num_m, num_n;         // tiles (of 128 * NCTA rows, 256 columns)
   int m_inner;              // 1: consecutive tile indices walk M first (logits), 0: N first
   int m_group;              // m_inner only: M tiles are walked in groups of this many (all N tiles of a group before
                             // the next group), so that the A rows of a group stay in L2 while B streams past
@@ -228,7 +233,7 @@ __device__ __forceinline__ void stage_f32_row(uint32_t buf, int lane, const floa
 }
 
 // ---------------------------------------------------------------------------------------------- the kernel
-template <int EPI, bool A_MN, bool B_MN>
+template <int EPI, bool A_MN, bool B_MN, int NCTA>
 __global__ void __launch_bounds__(kThreads, 1)
 k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
           const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
@@ -236,6 +241,9 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;            // SWIZZLE_128B tiles need 1024-byte alignment
   uint8_t* smem = smem_raw + (base - raw);
+  constexpr int kStages = num_stages(NCTA), kBBytes = b_bytes(NCTA), kStageBytes = stage_bytes(NCTA);
+  constexpr int BMT = BM * NCTA;                           // accumulator rows of one tile (all CTAs of the pair)
+  constexpr int BNC = BN / NCTA;                           // B columns this CTA stages
   const uint32_t sA = base, sB = base + kStages * kABytes;
   const uint32_t sEpi = base + kStages * kStageBytes;      // epilogue staging tiles (1024-byte aligned)
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + epi_stage_bytes(EPI));
@@ -250,9 +258,13 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // pair mode: rank of this CTA in its pair (0 = leader), tiles are dealt to pairs
+  const uint32_t rank = NCTA == 2 ? cluster_ctarank() : 0u;
+  const int walker = NCTA == 2 ? int(blockIdx.x >> 1) : int(blockIdx.x);
+  const int walkers = NCTA == 2 ? int(gridDim.x >> 1) : int(gridDim.x);
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), kEpiWarps); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), NCTA * kEpiWarps); }
     for (int q = 0; q < 4; ++q) { mbar_init(mfull_bar(q), 1); mbar_init(mempty_bar(q), 1); }
     *abort_flag = 0;
     fence_barrier_init();
@@ -261,11 +273,17 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     if constexpr (epi_stage_bytes(EPI) > 0) prefetch_tmap(&tmC);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tmem_relinquish();
+    if constexpr (NCTA == 2) {
+      tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (NCTA == 2) cluster_sync_all();   // the peer's mbarriers are initialised before anything signals them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -294,58 +312,70 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       constexpr int kAPol = EPI == kEpiLogits ? 2 : 0;
       constexpr int kBPol = EPI == kEpiDw ? 2 : 0;
       const uint64_t pol_last = l2_policy_evict_last();
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      // pair mode: the bytes of both CTAs are counted on the leader's barrier, which only the leader arms
+      // (the policy is a compile-time constant: a run-time choice here costs the producer about a tenth of its rate)
+      auto ld2 = [&](uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, auto keep) {
+        if constexpr (NCTA == 2) {
+          if constexpr (decltype(keep)::value) tma_pair_load_2d_hint(dst, tm, bar, c0, c1, pol_last);
+          else tma_pair_load_2d(dst, tm, bar, c0, c1);
+        } else {
+          if constexpr (decltype(keep)::value) tma_load_2d_hint(dst, tm, bar, c0, c1, pol_last);
+          else tma_load_2d(dst, tm, bar, c0, c1);
+        }
+      };
+      auto ld3 = [&](uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, int c2, auto keep) {
+        if constexpr (NCTA == 2) {
+          if constexpr (decltype(keep)::value) tma_pair_load_3d_hint(dst, tm, bar, c0, c1, c2, pol_last);
+          else tma_pair_load_3d(dst, tm, bar, c0, c1, c2);
+        } else {
+          if constexpr (decltype(keep)::value) tma_load_3d_hint(dst, tm, bar, c0, c1, c2, pol_last);
+          else tma_load_3d(dst, tm, bar, c0, c1, c2);
+        }
+      };
+      constexpr std::bool_constant<kAPol == 2> keepA{};
+      constexpr std::bool_constant<kBPol == 2> keepB{};
+      for (int tile = walker; tile < num_tiles && ok; tile += walkers) {
         int mi, ni;
         decode(tile, mi, ni);
-        const int m0 = p.m_off + mi * BM, n0 = ni * BN;
+        const int m0 = p.m_off + mi * BMT + int(rank) * BM, n0 = ni * BN + int(rank) * BNC;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait<true>(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kErrProducerWait)) { ok = false; break; }
-          const uint32_t bar = full_bar(stage);
-          mbar_arrive_expect_tx(bar, kStageBytes);
+          const uint32_t bar = NCTA == 2 ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), NCTA * kStageBytes);
           const uint32_t a_dst = sA + stage * kABytes, b_dst = sB + stage * kBBytes;
           const int k0 = kb * BK;
           if constexpr (A_MN) {
             if (p.a_3d) {
-              if constexpr (kAPol == 2) tma_load_3d_hint(a_dst, &tmA, bar, 0, k0, m0 >> 6, pol_last);
-              else tma_load_3d(a_dst, &tmA, bar, 0, k0, m0 >> 6);
+              ld3(a_dst, &tmA, bar, 0, k0, m0 >> 6, keepA);
             } else {
 #pragma unroll
-              for (int j = 0; j < BM / 64; ++j) {
-                if constexpr (kAPol == 2) tma_load_2d_hint(a_dst + j * kBoxBytesMN, &tmA, bar, m0 + j * 64, k0, pol_last);
-                else tma_load_2d(a_dst + j * kBoxBytesMN, &tmA, bar, m0 + j * 64, k0);
-              }
+              for (int j = 0; j < BM / 64; ++j) ld2(a_dst + j * kBoxBytesMN, &tmA, bar, m0 + j * 64, k0, keepA);
             }
           } else {
-            if constexpr (kAPol == 2) tma_load_2d_hint(a_dst, &tmA, bar, k0, m0, pol_last);
-            else tma_load_2d(a_dst, &tmA, bar, k0, m0);
+            ld2(a_dst, &tmA, bar, k0, m0, keepA);
           }
           if constexpr (B_MN) {
             if (p.b_3d) {
-              if constexpr (kBPol == 2) tma_load_3d_hint(b_dst, &tmB, bar, 0, k0, n0 >> 6, pol_last);
-              else tma_load_3d(b_dst, &tmB, bar, 0, k0, n0 >> 6);
+              ld3(b_dst, &tmB, bar, 0, k0, n0 >> 6, keepB);
             } else {
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j) {
-                if constexpr (kBPol == 2) tma_load_2d_hint(b_dst + j * kBoxBytesMN, &tmB, bar, n0 + j * 64, k0, pol_last);
-                else tma_load_2d(b_dst + j * kBoxBytesMN, &tmB, bar, n0 + j * 64, k0);
-              }
+              for (int j = 0; j < BNC / 64; ++j) ld2(b_dst + j * kBoxBytesMN, &tmB, bar, n0 + j * 64, k0, keepB);
             }
           } else {
-            if constexpr (kBPol == 2) tma_load_2d_hint(b_dst, &tmB, bar, k0, n0, pol_last);
-            else tma_load_2d(b_dst, &tmB, bar, k0, n0);
+            ld2(b_dst, &tmB, bar, k0, n0, keepB);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ------------------------------------------------------------------ UMMA issuer
-      constexpr uint32_t idesc = idesc_bf16_f32(BM, BN, A_MN, B_MN);
+    if (lane == 0 && rank == 0) {
+      // ------------------------------------------------------------------ UMMA issuer (pair mode: the leader only)
+      constexpr uint32_t idesc = idesc_bf16_f32(BMT, BN, A_MN, B_MN);
       int stage = 0; uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = walker; tile < num_tiles && ok; tile += walkers, ++it) {
         const int b = it & 1;
         if (!mbar_wait(tempty_bar(b), ((it >> 1) & 1u) ^ 1u, abort_flag, p.status, kErrTmemFreeWait)) break;
         tc_fence_after();
@@ -361,12 +391,18 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                                      : smem_desc_sw128(a_src + k * (UK * 2), 16, 1024);
             const uint64_t bd = B_MN ? smem_desc_sw128(b_src + k * (UK * 128), kBoxBytesMN, 1024)
                                      : smem_desc_sw128(b_src + k * (UK * 2), 16, 1024);
-            umma_bf16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+            if constexpr (NCTA == 2) umma_pair_bf16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+            else umma_bf16(d_tmem, ad, bd, idesc, (kb | k) != 0);
           }
-          umma_commit(empty_bar(stage));   // the stage is free again once these UMMAs have read it
+          // the stage is free again once these UMMAs have read it (pair mode: in both CTAs)
+          if constexpr (NCTA == 2) umma_pair_commit(empty_bar(stage), 3);
+          else umma_commit(empty_bar(stage));
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit(tfull_bar(b));   // accumulator of this tile complete
+        if (ok) {                            // accumulator of this tile complete
+          if constexpr (NCTA == 2) umma_pair_commit(tfull_bar(b), 3);
+          else umma_commit(tfull_bar(b));
+        }
       }
     }
   } else {
@@ -383,11 +419,11 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     const uint64_t store_policy = l2_policy_evict_first();   // the logits store is not read again by this kernel
     constexpr int kChunks = BN / 32 / 2;       // 32-column chunks per warp
     int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    for (int tile = walker; tile < num_tiles; tile += walkers, ++it) {
       const int b = it & 1;
       int mi, ni;
       decode(tile, mi, ni);
-      const int m0 = mi * BM, n0 = ni * BN;
+      const int m0 = mi * BMT + int(rank) * BM, n0 = ni * BN;
       const int grow = m0 + r_local;
       const bool row_ok = grow < p.M;
       const bool warp_rows_ok = m0 + quad * 32 < p.M;          // any row of this warp inside the matrix
@@ -463,7 +499,10 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       // the accumulator buffer may be overwritten by the UMMAs of the tile after next
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(b));
+      if (lane == 0) {
+        if constexpr (NCTA == 2) mbar_arrive_cluster(mapa_shared(tempty_bar(b), 0));   // the leader issues the UMMAs
+        else mbar_arrive(tempty_bar(b));
+      }
       if constexpr (EPI == kEpiLogits) {
         // the two halves of a row meet in shared memory; the left half merges (left, then right: a fixed order) and
         // writes the tile's partial. Hand-over by two mbarriers per quadrant, waited on with the bounded wait.
@@ -498,12 +537,16 @@ k_ce_umma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 
   // -------------------------------------------------------------------- teardown
   tc_fence_before();
-  __syncthreads();
+  // pair mode: neither CTA may leave (or free TMEM) while the other can still signal its barriers or read its shared
+  // memory; every wait above is bounded, so both CTAs reach this barrier
+  if constexpr (NCTA == 2) cluster_sync_all();
+  else __syncthreads();
   if (warp == 1) {
     __syncwarp();
     if (*abort_flag) __nanosleep(200000);   // an expired wait: let copies and UMMAs in flight land before TMEM goes
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (NCTA == 2) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -604,9 +647,9 @@ CUtensorMap tmap_mn_a(const void* base, int64_t K, int64_t MN, int64_t ld, int& 
   is3d = MN % 64 == 0;
   return is3d ? tmap_mnmajor_3d(base, K, MN, ld, BM / 64) : tmap_mnmajor(base, K, MN, ld);
 }
-CUtensorMap tmap_mn_b(const void* base, int64_t K, int64_t MN, int64_t ld, int& is3d) {
+CUtensorMap tmap_mn_b(const void* base, int64_t K, int64_t MN, int64_t ld, int& is3d, int ncta) {
   is3d = MN % 64 == 0;
-  return is3d ? tmap_mnmajor_3d(base, K, MN, ld, BN / 64) : tmap_mnmajor(base, K, MN, ld);
+  return is3d ? tmap_mnmajor_3d(base, K, MN, ld, BN / ncta / 64) : tmap_mnmajor(base, K, MN, ld);
 }
 
 // epilogue staging tile as a tensor-map box: 32 rows x 32 columns (f32: 128-byte rows, SWIZZLE_128B; bf16: 64-byte
@@ -615,52 +658,72 @@ CUtensorMap tmap_epilogue(void* base, int64_t rows, int64_t cols, int64_t ld, bo
   return make_tmap(base, uint64_t(cols), uint64_t(rows), ld, 32, 32, f32, !f32);
 }
 
-template <int EPI, bool A_MN, bool B_MN>
-void launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
-            cudaStream_t st, int sm_reserve = 0) {
-  auto kernel = k_ce_umma<EPI, A_MN, B_MN>;
-  constexpr int kSmem = smem_bytes(EPI);
+template <int EPI, bool A_MN, bool B_MN, int NCTA>
+void launch_n(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+              cudaStream_t st, int sm_reserve) {
+  auto kernel = k_ce_umma<EPI, A_MN, B_MN, NCTA>;
+  constexpr int kSmem = smem_bytes(EPI, NCTA);
   static_assert(kSmem <= 232448, "dynamic shared memory beyond the 227 KiB a CTA may use");
   NM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
   const int tiles = p.num_m * p.num_n;
-  const int sms = std::max(1, sm_count() - std::max(0, sm_reserve));
-  const int grid = tiles < sms ? tiles : sms;
-  kernel<<<grid, kThreads, kSmem, st>>>(ta, tb, tc, p);
-  NM_CUDA(cudaGetLastError());
+  const int walkers = std::max(1, (sm_count() - std::max(0, sm_reserve)) / NCTA);   // CTAs, or pairs of CTAs
+  const int grid = NCTA * std::min(tiles, walkers);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(unsigned(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = NCTA; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = NCTA == 2 ? 1 : 0;
+  NM_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, p));
 }
+template <int EPI, bool A_MN, bool B_MN>
+void launch(int ncta, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+            cudaStream_t st, int sm_reserve = 0) {
+  if (ncta == 2) launch_n<EPI, A_MN, B_MN, 2>(ta, tb, tc, p, st, sm_reserve);
+  else launch_n<EPI, A_MN, B_MN, 1>(ta, tb, tc, p, st, sm_reserve);
+}
+
+// CTAs per tile for the three contractions (1, or 2 = pair mode), per process
+int g_ncta[3] = {1, 1, 1};
 
 }  // namespace
 
 void launch_logits(const LogitsArgs& a, cudaStream_t st) {
   if (a.rows <= 0) return;
   GemmParams p{};
+  const int ncta = g_ncta[0], bmt = BM * ncta;
   p.M = a.rows; p.N = a.V; p.K = a.D; p.m_off = 0;
-  p.num_m = (a.rows + BM - 1) / BM; p.num_n = (a.V + BN - 1) / BN; p.m_inner = 1;
+  p.num_m = (a.rows + bmt - 1) / bmt; p.num_n = (a.V + BN - 1) / BN; p.m_inner = 1;
   // rows are walked in groups whose x tiles (group x 128 x D bf16) take about 16 MiB of L2: x is then read from HBM
   // once per launch and W once per group, instead of x once per vocabulary tile
-  p.m_group = int(std::max<int64_t>(1, std::min<int64_t>(p.num_m, (int64_t(16) << 20) / (int64_t(BM) * a.D * 2))));
+  p.m_group = int(std::max<int64_t>(1, std::min<int64_t>(p.num_m, (int64_t(16) << 20) / (int64_t(bmt) * a.D * 2))));
   p.status = a.status;
   p.store = a.store; p.ldS = a.ldS; p.store_f32 = a.store_f32;
   p.tmax = a.tmax; p.tsum = a.tsum; p.ldT = a.ldT; p.zt = a.zt; p.targets = a.targets; p.bias = a.bias;
   const CUtensorMap ta = tmap_kmajor(a.x, a.rows, a.D, a.D, BM);
-  const CUtensorMap tb = tmap_kmajor(a.w, a.V, a.D, a.D, BN);
+  const CUtensorMap tb = tmap_kmajor(a.w, a.V, a.D, a.D, BN / ncta);
   // the bf16 store leaves by TMA; without one (forward only, f32 store) the map is unused
   const CUtensorMap tc = (a.store && !a.store_f32) ? tmap_epilogue(a.store, a.rows, a.V, a.ldS, false) : ta;
-  launch<kEpiLogits, false, false>(ta, tb, tc, p, st);
+  launch<kEpiLogits, false, false>(ncta, ta, tb, tc, p, st);
 }
 
 void launch_dgrad(const DgradArgs& a, cudaStream_t st) {
   if (a.rows <= 0) return;
   GemmParams p{};
+  const int ncta = g_ncta[1], bmt = BM * ncta;
   p.M = a.rows; p.N = a.D; p.K = a.V; p.m_off = 0;
-  p.num_m = (a.rows + BM - 1) / BM; p.num_n = (a.D + BN - 1) / BN; p.m_inner = 0;
+  p.num_m = (a.rows + bmt - 1) / bmt; p.num_n = (a.D + BN - 1) / BN; p.m_inner = 0;
   p.m_group = 1;
   p.status = a.status;
   p.scale = a.scale; p.dx_old = a.dx_old; p.dx_out = a.dx_out; p.acc_mode = a.dx_old ? a.acc_mode : 0;
   p.out_f32 = a.out_f32; p.ldo = a.D;
   const CUtensorMap ta = tmap_kmajor(a.n, a.rows, a.V, a.ldn, BM);
-  const CUtensorMap tb = tmap_mn_b(a.w, a.V, a.D, a.ldw, p.b_3d);
-  launch<kEpiDx, false, true>(ta, tb, ta, p, st, a.sm_reserve);
+  const CUtensorMap tb = tmap_mn_b(a.w, a.V, a.D, a.ldw, p.b_3d, ncta);
+  launch<kEpiDx, false, true>(ncta, ta, tb, ta, p, st, a.sm_reserve);
 }
 
 void launch_wgrad(const WgradArgs& a, cudaStream_t st) {
@@ -668,15 +731,20 @@ void launch_wgrad(const WgradArgs& a, cudaStream_t st) {
   NM_REQUIRE(a.v0 % BM == 0 && (a.v1 % BM == 0 || a.v1 == a.V) && a.v1 <= a.V,
              "fused CE: a dW vocabulary range must start and end on multiples of 128 (or end at V)");
   GemmParams p{};
+  const int ncta = g_ncta[2], bmt = BM * ncta;
   p.M = a.v1 - a.v0; p.N = a.D; p.K = a.rows; p.m_off = a.v0;
-  p.num_m = (p.M + BM - 1) / BM; p.num_n = (a.D + BN - 1) / BN; p.m_inner = 0;
+  p.num_m = (p.M + bmt - 1) / bmt; p.num_n = (a.D + BN - 1) / BN; p.m_inner = 0;
   p.m_group = 1;
   p.status = a.status;
   p.scale = a.scale; p.dw = a.dw; p.round_bf16 = a.round_bf16;
   const CUtensorMap ta = tmap_mn_a(a.n, a.rows, a.V, a.ldn, p.a_3d);
-  const CUtensorMap tb = tmap_mn_b(a.x, a.rows, a.D, a.ldx, p.b_3d);
+  const CUtensorMap tb = tmap_mn_b(a.x, a.rows, a.D, a.ldx, p.b_3d, ncta);
   const CUtensorMap tc = tmap_epilogue(a.dw, a.V, a.D, a.D, true);
-  launch<kEpiDw, true, true>(ta, tb, tc, p, st, a.sm_reserve);
+  launch<kEpiDw, true, true>(ncta, ta, tb, tc, p, st, a.sm_reserve);
+}
+
+void set_cta_pair(int logits, int dgrad, int wgrad) {
+  g_ncta[0] = logits ? 2 : 1; g_ncta[1] = dgrad ? 2 : 1; g_ncta[2] = wgrad ? 2 : 1;
 }
 
 void launch_wait_timeout_probe(uint32_t* status, long long limit_cycles, int* saw_abort, cudaStream_t st) {
@@ -688,22 +756,24 @@ void launch_wait_timeout_probe(uint32_t* status, long long limit_cycles, int* sa
 
 void launch_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,
                       int N, int K, uint32_t* status, cudaStream_t st) {
-  NM_REQUIRE(kind >= 0 && kind <= 2, "test gemm: kind 0, 1 or 2");
+  NM_REQUIRE((kind & ~4) >= 0 && (kind & ~4) <= 2, "test gemm: kind 0, 1 or 2, plus 4 for the CTA-pair form");
   NM_REQUIRE(M > 0 && N > 0 && K > 0, "test gemm: M, N, K > 0");
+  const int ncta = (kind & 4) ? 2 : 1, bmt = BM * ncta;
+  kind &= ~4;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.m_off = 0;
-  p.num_m = (M + BM - 1) / BM; p.num_n = (N + BN - 1) / BN;
+  p.num_m = (M + bmt - 1) / bmt; p.num_n = (N + BN - 1) / BN;
   p.m_inner = kind == 0; p.m_group = 3;          // the grouped walk is exercised by the K-major test
   p.status = status; p.c = c; p.ldc = ldc;
   if (kind == 0) {
     const CUtensorMap ta = tmap_kmajor(a, M, K, lda, BM);
-    launch<kEpiTest, false, false>(ta, tmap_kmajor(b, N, K, ldb, BN), ta, p, st);
+    launch<kEpiTest, false, false>(ncta, ta, tmap_kmajor(b, N, K, ldb, BN / ncta), ta, p, st);
   } else if (kind == 1) {
     const CUtensorMap ta = tmap_kmajor(a, M, K, lda, BM);
-    launch<kEpiTest, false, true>(ta, tmap_mn_b(b, K, N, ldb, p.b_3d), ta, p, st);
+    launch<kEpiTest, false, true>(ncta, ta, tmap_mn_b(b, K, N, ldb, p.b_3d, ncta), ta, p, st);
   } else {
     const CUtensorMap ta = tmap_mn_a(a, K, M, lda, p.a_3d);
-    launch<kEpiTest, true, true>(ta, tmap_mn_b(b, K, N, ldb, p.b_3d), ta, p, st);
+    launch<kEpiTest, true, true>(ncta, ta, tmap_mn_b(b, K, N, ldb, p.b_3d, ncta), ta, p, st);
   }
 }
 

@@ -97,7 +97,11 @@ void launch_wgrad(const WgradArgs& a, cudaStream_t st);
 // unit-test entry: one CTA whose bounded wait runs out after `limit_cycles` (<= 2e6) on a barrier nobody completes
 void launch_wait_timeout_probe(uint32_t* status, long long limit_cycles, int* saw_abort, cudaStream_t st);
 
-// unit-test entry: C f32 [M, N] = A B^T in the three operand layouts (kind 0 K/K, 1 K/MN, 2 MN/MN)
+// CTAs per accumulator tile of the three contractions: 0 = one CTA per 128 x 256 tile, 1 = a pair of CTAs (cluster of
+// two, one UMMA of M = 256 over both) per 256 x 256 tile. Process-wide; not to be changed while a call is in flight.
+void set_cta_pair(int logits, int dgrad, int wgrad);
+
+// unit-test entry: C f32 [M, N] = A B^T in the three operand layouts (kind 0 K/K, 1 K/MN, 2 MN/MN; + 4: CTA pairs)
 void launch_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,
                       int N, int K, uint32_t* status, cudaStream_t st);
 

@@ -7,6 +7,8 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <string>
 
@@ -54,6 +56,16 @@ const NcclApi& nccl() {
 
 }  // namespace
 
+int comm_sms() {
+  static const int v = [] {
+    const char* e = std::getenv("NM_COMM_SMS");
+    if (!e || !*e) return kCommSms;
+    const int n = std::atoi(e);
+    return n < 4 ? 4 : (n > 64 ? 64 : n);
+  }();
+  return v;
+}
+
 void nccl_check(int err, const char* expr, const char* where) {
   if (err == 0) return;
   const char* s = nccl().GetErrorString ? nccl().GetErrorString(static_cast<ncclResult_t>(err)) : "?";
@@ -80,7 +92,7 @@ Comm::Comm(const void* id128_host, int nranks, int rank) : nranks_(nranks), rank
     // the collectives of this communicator run beside the persistent tcgen05 kernels, which leave kCommSms SMs free
     // while a reduction is in flight: cap NCCL at that many CTAs
     ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
-    cfg.maxCTAs = kCommSms;
+    cfg.maxCTAs = comm_sms();
     NM_NCCL(nccl().CommInitRankConfig(&c, nranks, id, rank, &cfg));
   } else {
     NM_NCCL(nccl().CommInitRank(&c, nranks, id, rank));

@@ -35,6 +35,7 @@ SIGS = {
     "nm_ce_profile_enable": (I32, [I32]),
     "nm_ce_profile_read": (I32, [VP, VP]),
     "nm_ce_test_wait_timeout": (I32, [VP, I64, VP, VP]),
+    "nm_ce_set_cta_pair": (I32, [I32, I32, I32]),
     "nm_ce_test_gemm": (I32, [I32, VP, I64, VP, I64, VP, I64, I32, I32, I32, VP, VP]),
     "nm_rmsnorm_fwd": (I32, [I32, I32, VP, VP, VP, VP, I64, I32, F32, VP]),
     "nm_norm_partial_rows": (I64, [I64]),
