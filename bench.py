@@ -270,6 +270,9 @@ def main():
     ap.add_argument("--buckets", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (small cases for profiling)")
     ap.add_argument("--cta-pair", default="", help="three digits (logits, dX, dW): 1 = a CTA pair per tile, e.g. 011")
+    ap.add_argument("--zero1", action="store_true",
+                    help="reduce dW to its owners (reduce-scatter), AdamH on owned elements and all-gather of the bf16 "
+                         "head inside every step, instead of the dW all-reduce (the optimizer then is in the timing)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg")
     args = ap.parse_args()
@@ -336,8 +339,21 @@ def main():
         if cfg["reduce"] == "bf16":
             staging = torch.empty(V, D, dtype=torch.bfloat16, device=dev)
         reducer = ctypes.c_void_p()
-        lib.nm_grad_reducer_create(comm, nmce.ptr(dw), V, D, args.buckets, 1 if cfg["reduce"] == "bf16" else 0,
-                                   nmce.ptr(staging), ctypes.byref(reducer))
+        if args.zero1:
+            lib.nm_grad_reducer_create_owners(comm, nmce.ptr(dw), V, D, args.buckets, ctypes.byref(reducer))
+        else:
+            lib.nm_grad_reducer_create(comm, nmce.ptr(dw), V, D, args.buckets, 1 if cfg["reduce"] == "bf16" else 0,
+                                       nmce.ptr(staging), ctypes.byref(reducer))
+    head_opt = None
+    if args.zero1:
+        head_opt = ctypes.c_void_p()
+        lib.nm_head_adamh_create(V, D, reducer, ctypes.byref(head_opt))
+        n_own = int(lib.nm_head_adamh_owned_elems(head_opt))
+        p_own = torch.empty(n_own, dtype=torch.float32, device=dev)
+        mu_own = torch.zeros(n_own, dtype=torch.float32, device=dev)
+        nu_own = torch.zeros(n_own, dtype=torch.float32, device=dev)
+        lib.nm_head_adamh_init_master(head_opt, nmce.ptr(W), nmce.ptr(p_own), sp)
+        opt_t = [0]
 
     def ce(x_in, y_in, wt_in, r, last):
         lib.nm_fused_linear_ce_ex(1, 0, 1, 1, nmce.ptr(x_in), nmce.ptr(W), nmce.ptr(y_in), nmce.ptr(wt_in),
@@ -380,6 +396,10 @@ def main():
                 ev = torch.cuda.Event(enable_timing=True)
                 ev.record(stream)
                 comm_events.append(ev)
+        if head_opt:
+            opt_t[0] += 1     # a tiny learning rate: the master copy moves every step, the synthetic loss stays where it is
+            lib.nm_head_adamh_step(head_opt, opt_t[0], 1e-6, 0.9, 0.98, 1e-20, 1.0, 1.0, nmce.ptr(dw), nmce.ptr(p_own),
+                                   nmce.ptr(mu_own), nmce.ptr(nu_own), nmce.ptr(W), sp)
 
     comm_events = None       # pairs of events around the wait for the dW all-reduce (its exposed, non-overlapped part)
 
@@ -399,6 +419,8 @@ def main():
         launches_per_step += args.buckets - 1
     if reducer and cfg["reduce"] == "bf16":
         launches_per_step += 2 * args.buckets              # casts around the bf16 all-reduce
+    if args.zero1:
+        launches_per_step += 5                             # AdamH: clip norm + its partial sum, moments + partial sums, apply
 
     # ---------------------------------------------------------------- device-resident timing (value)
     for _ in range(args.warmup):
@@ -505,6 +527,8 @@ def main():
         cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
                "sample": f"first {n} rows of the batch, full vocabulary, {secs:.1f} s (cost is linear in rows)"}
 
+    if head_opt:
+        lib.nm_head_adamh_destroy(head_opt)
     if reducer:
         lib.nm_grad_reducer_destroy(reducer)
         lib.nm_comm_destroy(comm)
@@ -538,8 +562,12 @@ def main():
         "config": {"workload": WORKLOAD[args.config] + (f" [tokens overridden to {T}]" if args.tokens > 0 else ""),
                    "tokens_per_gpu": R * T, "hidden": D, "vocab": V,
                    "chunk_rows": chunk, "readouts": R, "parallelism": f"dp{world} (rows sharded, W replicated)",
-                   "dw_allreduce": (f"{cfg['reduce']}, {args.buckets} buckets, overlapped with the last dX" if world > 1
-                                    else "none (1 GPU)"),
+                   "dw_allreduce": ((f"f32 reduce-scatter to owners, {args.buckets} buckets, overlapped with the last dX"
+                                     if args.zero1 else
+                                     f"{cfg['reduce']}, {args.buckets} buckets, overlapped with the last dX")
+                                    if world > 1 else "none (1 GPU)"),
+                   "optimizer_in_step": ("AdamH of the head on owned elements + bf16 all-gather (ZeRO-1)"
+                                         if args.zero1 else None),
                    "exposed_allreduce_ms_per_step_rank0": exposed_comm_ms,
                    "allreduce_wait_ms_per_step_by_rank": exposed_by_rank,
                    "l2": "inputs (x, W, logits store: > 5 GB per step) exceed the 126 MB L2; no flush needed",

@@ -1,0 +1,51 @@
+/* C ABI of the LM head's AdamH update (the optimizer step that consumes the fused cross-entropy's dW). Conventions as
+ * in capi.h: device pointers, `stream` is a cudaStream_t passed as void* (NULL = legacy default stream), int status
+ * returns (NM_OK / NM_ERR_*), message in nm_last_error(). */
+#pragma once
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* reference include/marincpp/capi.h:107-110 (src/optim/capi_optim.cpp:202-219): one AdamH update of one 2-D tensor
+ * p[rows, cols] f32 (p16: optional bf16 copy of the new p) from gradient g and moments mu, nu, at update count t >= 1
+ * with learning rate eta; when `clip` is non-zero the gradient is first scaled as (g / clip_gn) * max_norm.
+ * block_of_row / block_lr_mult / block_frozen (row blocks with their own learning rates and norms) are not
+ * supported here: pass NULL, NULL, NULL, 0 (anything else returns NM_ERR_INVALID). Unlike the reference's, this call
+ * does not synchronise the stream. */
+int nm_adamh_update(float* p, void* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
+                    float eta, float b1, float b2, float eps, float clip_gn, int clip, float max_norm,
+                    const int32_t* block_of_row, const float* block_lr_mult, const uint8_t* block_frozen,
+                    int n_blocks, void* stream);
+
+/* ---- ZeRO-1 form (the design of the reference's include/marincpp/comm.hpp:22-71; no C entry points there) -------- */
+
+/* nm_grad_reducer_create (capi_ce.h) with a reduction to owners: every bucket is reduce-scattered (f32), rank r keeps
+ * the summed gradient on its element range of each bucket only. */
+int nm_grad_reducer_create_owners(void* comm, float* grad, int V, int D, int n_buckets, void** reducer_out);
+
+/* An updater for the head [V, D]. reducer: NULL (one rank owns everything) or a handle from
+ * nm_grad_reducer_create_owners over the same gradient. */
+int nm_head_adamh_create(int V, int D, void* reducer, void** out);
+int nm_head_adamh_destroy(void* h);
+/* number of f32 elements of the caller's p / mu / nu arrays (owned elements only) */
+int64_t nm_head_adamh_owned_elems(void* h);
+/* the owned ranges: up to `cap` entries of (offset into the flat tensor, offset into the compact arrays, length) */
+int nm_head_adamh_ranges(void* h, int cap, int64_t* global_off_host, int64_t* compact_off_host, int64_t* len_host,
+                         int* n_out);
+/* p_owned = f32(w16) on the owned ranges */
+int nm_head_adamh_init_master(void* h, const void* w16, float* p_owned, void* stream);
+/* One update: clip by the head's own gradient norm (max_grad_norm <= 0: none), AdamH on owned elements, bf16 copy
+ * into w16 and (with a reducer) all-gather of w16. Waits for the reducer's buckets on `stream` first. */
+int nm_head_adamh_step(void* h, int64_t t, float eta, float b1, float b2, float eps, float max_grad_norm,
+                       float grad_scale, const float* grad, float* p_owned, float* mu_owned, float* nu_owned,
+                       void* w16, void* stream);
+/* the last step's scalars (4 doubles: sum g^2, sum p^2, sum a^2, sum p a over the whole tensor) copied to the host
+ * after the work on `stream` (synchronises that stream) */
+int nm_head_adamh_scalars(void* h, double* out4_host, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -33,7 +33,14 @@ class Comm {
   int nranks() const { return nranks_; }
   int rank() const { return rank_; }
   cudaStream_t stream() const { return stream_; }              // the communication stream
-  void allreduce_sum(void* buf, int64_t n, DType dt, cudaStream_t st);   // in place; dt f32 or bf16
+  void allreduce_sum(void* buf, int64_t n, DType dt, cudaStream_t st);   // in place; dt f32, bf16 or f64
+  // buf holds nranks * count f32 elements; afterwards elements [rank * count, (rank + 1) * count) hold the sum over
+  // ranks (in place); the other parts are unspecified
+  void reduce_scatter_sum_f32(float* buf, int64_t count, cudaStream_t st);
+  // every rank's part [rank * count, (rank + 1) * count) of buf is gathered into buf on every rank (in place)
+  void allgather(void* buf, int64_t count, DType dt, cudaStream_t st);
+  void group_start();
+  void group_end();
  private:
   void* comm_ = nullptr;
   cudaStream_t stream_ = nullptr;
@@ -49,12 +56,23 @@ class GradReducer {
   // grad [V, D] f32; n_buckets contiguous vocabulary ranges whose sizes are multiples of 128 rows (the last takes the
   // remainder). reduce_dtype f32: in place. bf16: each bucket is cast into `staging` (V * D bf16, caller owned),
   // all-reduced there and cast back (wire bytes halved; the sum is then a bf16 sum).
-  GradReducer(Comm& comm, float* grad, int V, int D, int n_buckets, DType reduce_dtype, void* staging);
+  // to_owners (ZeRO-1, the reference's include/marincpp/comm.hpp:36-44 design): each bucket is reduce-scattered
+  // instead of all-reduced: rank r ends up with the sum on elements [r, r + 1) * n / nranks of the bucket's n = rows * D
+  // elements only (its owned range; f32 only, n must divide by nranks), for an optimizer that updates owned elements
+  // and all-gathers the updated bf16 parameters (HeadAdamH). Wire bytes per parameter 4 + 2 instead of 8.
+  GradReducer(Comm& comm, float* grad, int V, int D, int n_buckets, DType reduce_dtype, void* staging,
+              bool to_owners = false);
   ~GradReducer();
   GradReducer(const GradReducer&) = delete;
   GradReducer& operator=(const GradReducer&) = delete;
   int n_buckets() const { return int(v0_.size()); }
   void range(int b, int& v0, int& v1) const { v0 = v0_[b]; v1 = v1_[b]; }
+  bool to_owners() const { return to_owners_; }
+  Comm& comm() const { return comm_; }
+  int V() const { return V_; }
+  int D() const { return D_; }
+  // to_owners: this rank's element range of bucket b (offset into grad, length)
+  void owned_range(int b, int64_t& offset, int64_t& len) const;
   // Bucket b of grad is final on `compute`: its all-reduce is enqueued on the communication stream behind an event.
   void bucket_ready(int b, cudaStream_t compute);
   void reduce_all(cudaStream_t compute);       // every bucket, after the work already on `compute`
@@ -65,6 +83,7 @@ class GradReducer {
   int V_, D_;
   DType dtype_;
   void* staging_;
+  bool to_owners_ = false;
   std::vector<int> v0_, v1_;
   std::vector<cudaEvent_t> ready_;
   cudaEvent_t done_ = nullptr;

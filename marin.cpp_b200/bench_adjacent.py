@@ -88,6 +88,29 @@ def main():
     report("ce_dlogits (bf16 store, in place)",
            timed(lambda: lib.nm_ce_dlogits(1, p(store), V, p(lse), p(gsc), p(tgt), R, V, None)), 4 * R * V,
            f"{R} x {V} bf16")
+    del store
+    # AdamH of the head, whole tensor on one GPU (N = 1) and the share of one of 8 ranks (8 owned ranges): per element
+    # it reads g, p, mu, nu and writes mu, nu (pass 1: 24 B), reads p, mu, nu and writes p and its bf16 copy (pass 2:
+    # 18 B), plus 4 B for the clip norm's read of g = 46 B
+    import ctypes
+    Dh = 2048
+    for label, n_el in (("whole head, 1 rank", V * Dh), ("owned share of 1 of 8 ranks", V * Dh // 8)):
+        rows = n_el // Dh
+        P_ = torch.randn(rows, Dh, generator=g, device="cuda") * 0.02
+        G_ = torch.randn(rows, Dh, generator=g, device="cuda") * 1e-4
+        M_ = torch.zeros(rows, Dh, device="cuda")
+        V_ = torch.zeros(rows, Dh, device="cuda")
+        W_ = torch.empty(rows, Dh, dtype=bf, device="cuda")
+        h = ctypes.c_void_p()
+        lib.nm_head_adamh_create(rows, Dh, None, ctypes.byref(h))
+        step = [0]
+
+        def one():
+            step[0] += 1
+            lib.nm_head_adamh_step(h, step[0], 0.02, 0.9, 0.98, 1e-20, 1.0, 1.0, p(G_), p(P_), p(M_), p(V_), p(W_), None)
+        report(f"head_adamh_step ({label})", timed(one), 46 * n_el, f"{rows} x {Dh} f32")
+        lib.nm_head_adamh_destroy(h)
+        del P_, G_, M_, V_, W_
 
 
 if __name__ == "__main__":

@@ -23,6 +23,10 @@ struct NcclApi {
   ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;   // optional
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
   std::string error;
 };
@@ -48,6 +52,10 @@ const NcclApi& nccl() {
         reinterpret_cast<decltype(api.CommInitRankConfig)>(dlsym(h, "ncclCommInitRankConfig"));
     api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
     api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
+    api.ReduceScatter = reinterpret_cast<decltype(api.ReduceScatter)>(sym("ncclReduceScatter"));
+    api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+    api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
+    api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
     api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
   });
   if (!api.error.empty()) throw DeviceError("comm: " + api.error);
@@ -106,12 +114,33 @@ Comm::~Comm() {
   if (comm_) nccl().CommDestroy(static_cast<ncclComm_t>(comm_));
 }
 
+namespace {
+ncclDataType_t nccl_type(DType dt) {
+  NM_REQUIRE(dt == DType::f32 || dt == DType::bf16 || dt == DType::f64, "comm: f32, bf16 or f64 elements");
+  return dt == DType::f32 ? ncclFloat32 : (dt == DType::bf16 ? ncclBfloat16 : ncclFloat64);
+}
+}  // namespace
+
 void Comm::allreduce_sum(void* buf, int64_t n, DType dt, cudaStream_t st) {
-  NM_REQUIRE(dt == DType::f32 || dt == DType::bf16, "comm: all-reduce of f32 or bf16");
   if (n <= 0) return;
-  NM_NCCL(nccl().AllReduce(buf, buf, size_t(n), dt == DType::f32 ? ncclFloat32 : ncclBfloat16, ncclSum,
+  NM_NCCL(nccl().AllReduce(buf, buf, size_t(n), nccl_type(dt), ncclSum, static_cast<ncclComm_t>(comm_), st));
+}
+
+void Comm::reduce_scatter_sum_f32(float* buf, int64_t count, cudaStream_t st) {
+  if (count <= 0) return;
+  NM_NCCL(nccl().ReduceScatter(buf, buf + int64_t(rank_) * count, size_t(count), ncclFloat32, ncclSum,
+                               static_cast<ncclComm_t>(comm_), st));
+}
+
+void Comm::allgather(void* buf, int64_t count, DType dt, cudaStream_t st) {
+  if (count <= 0) return;
+  const char* base = static_cast<const char*>(buf);
+  NM_NCCL(nccl().AllGather(base + int64_t(rank_) * count * int64_t(dtype_size(dt)), buf, size_t(count), nccl_type(dt),
                            static_cast<ncclComm_t>(comm_), st));
 }
+
+void Comm::group_start() { NM_NCCL(nccl().GroupStart()); }
+void Comm::group_end() { NM_NCCL(nccl().GroupEnd()); }
 
 int grad_bucket_ranges(int V, int n_buckets, std::vector<int>& v0, std::vector<int>& v1) {
   NM_REQUIRE(V > 0, "grad reducer: V > 0");
@@ -131,12 +160,18 @@ int grad_bucket_ranges(int V, int n_buckets, std::vector<int>& v0, std::vector<i
   return nb;
 }
 
-GradReducer::GradReducer(Comm& comm, float* grad, int V, int D, int n_buckets, DType reduce_dtype, void* staging)
-    : comm_(comm), grad_(grad), V_(V), D_(D), dtype_(reduce_dtype), staging_(staging) {
+GradReducer::GradReducer(Comm& comm, float* grad, int V, int D, int n_buckets, DType reduce_dtype, void* staging,
+                         bool to_owners)
+    : comm_(comm), grad_(grad), V_(V), D_(D), dtype_(reduce_dtype), staging_(staging), to_owners_(to_owners) {
   NM_REQUIRE(grad && V > 0 && D > 0, "grad reducer: grad, V, D required");
   NM_REQUIRE(reduce_dtype == DType::f32 || (reduce_dtype == DType::bf16 && staging),
              "grad reducer: reduce dtype f32, or bf16 with a staging buffer");
+  NM_REQUIRE(!to_owners || reduce_dtype == DType::f32, "grad reducer: the reduction to owners is f32");
   grad_bucket_ranges(V, n_buckets, v0_, v1_);
+  if (to_owners)
+    for (size_t b = 0; b < v0_.size(); ++b)
+      NM_REQUIRE((int64_t(v1_[b] - v0_[b]) * D) % comm.nranks() == 0,
+                 "grad reducer: with a reduction to owners every bucket's element count must divide by the rank count");
   ready_.resize(v0_.size());
   for (auto& e : ready_) NM_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   NM_CUDA(cudaEventCreateWithFlags(&done_, cudaEventDisableTiming));
@@ -155,7 +190,9 @@ void GradReducer::bucket_ready(int b, cudaStream_t compute) {
   NM_CUDA(cudaStreamWaitEvent(cs, ready_[b], 0));
   float* g = grad_ + int64_t(v0_[b]) * D_;
   const int64_t n = int64_t(v1_[b] - v0_[b]) * D_;
-  if (dtype_ == DType::f32) {
+  if (to_owners_) {
+    comm_.reduce_scatter_sum_f32(g, n / comm_.nranks(), cs);
+  } else if (dtype_ == DType::f32) {
     comm_.allreduce_sum(g, n, DType::f32, cs);
   } else {
     uint16_t* s = static_cast<uint16_t*>(staging_) + int64_t(v0_[b]) * D_;
@@ -164,6 +201,13 @@ void GradReducer::bucket_ready(int b, cudaStream_t compute) {
     ce::launch_bf16_to_f32(s, g, n, cs);
   }
   NM_CUDA(cudaEventRecord(done_, cs));
+}
+
+void GradReducer::owned_range(int b, int64_t& offset, int64_t& len) const {
+  NM_REQUIRE(b >= 0 && b < n_buckets(), "grad reducer: bucket index");
+  const int64_t n = int64_t(v1_[b] - v0_[b]) * D_;
+  len = to_owners_ ? n / comm_.nranks() : n;
+  offset = int64_t(v0_[b]) * D_ + (to_owners_ ? int64_t(comm_.rank()) * len : 0);
 }
 
 void GradReducer::reduce_all(cudaStream_t compute) {

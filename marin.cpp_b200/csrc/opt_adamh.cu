@@ -1,0 +1,251 @@
+// AdamH update of the LM head over the element ranges a rank owns (ZeRO-1), as two streaming passes plus scalar
+// reductions. The reference runs it as three passes over the owned slices (src/kernels/optim/optk_adam.cu:84-221:
+// moments + sum p^2 + sum a^2, then sum w^2, then apply); here pass 1 also accumulates sum p a, so that
+//     sum w^2 = sum p^2 - 2 c sum p a + c^2 sum a^2,   c = eta n / max(m, 1e-10),   w = p - c a
+// is known without reading p, mu, nu a second time: 24 + 18 = 42 bytes per element instead of 24 + 12 + 18 = 54.
+// Element arithmetic keeps the reference's operation order with explicitly rounded f32 operations
+// (optk_adam.cu:19-26,178-199): mu, nu come out bit-identical; p differs only through the norms' summation order.
+// Norms are f64 sums of f32-rounded squares, rounded to f32 once before the f32 square root (optk_common.cuh:28-30).
+// All kernels are HBM-bound streaming kernels: float4 accesses, 256 threads, grid (blocks per range, ranges).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "opt_internal.hpp"
+
+namespace nm::opt {
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float sub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float dvd(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ float norm_of(double sumsq) { return __fsqrt_rn(static_cast<float>(sumsq)); }
+__device__ __forceinline__ double sq(float x) { return static_cast<double>(mul(x, x)); }
+__device__ __forceinline__ float fmax_nan(float a, float b) { return (a != a || a > b) ? a : b; }
+
+// fixed-order block sum (butterfly inside each warp, then warp 0 over the warp sums); valid in thread 0
+__device__ __forceinline__ double block_sum(double v) {
+  __shared__ double ws[kThreads / 32];
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) ws[w] = v;
+  __syncthreads();
+  double s = lane < kThreads / 32 ? ws[lane] : 0.0;
+  if (w == 0)
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  return s;
+}
+
+struct Clip {
+  bool on;
+  float gn, max_norm;
+};
+// clip_mode 0: none; 1: the caller's (clip_gn, clip); 2: gn from the global sum of squares in scal[kSumG]
+__device__ __forceinline__ Clip clip_of(const Hyper& h, const double* scal) {
+  if (h.clip_mode == 1) return Clip{h.clip != 0, h.clip_gn, h.max_norm};
+  if (h.clip_mode == 2) {
+    const float gn = norm_of(scal[kSumG]);
+    return Clip{!(gn < h.max_norm), gn, h.max_norm};   // optax clips unless gn < max (equality clips too)
+  }
+  return Clip{false, 1.f, 1.f};
+}
+__device__ __forceinline__ float clipped(float g, const Hyper& h, const Clip& c) {
+  const float gi = mul(g, h.grad_scale);
+  return c.on ? mul(dvd(gi, c.gn), c.max_norm) : gi;
+}
+__device__ __forceinline__ float adam_dir(float mu, float nu, const Hyper& h) {
+  return dvd(mu, mul(h.bc1, add(__fsqrt_rn(dvd(nu, h.bc2)), h.eps)));
+}
+
+// A range is walked in float4 units when its global and compact offsets are multiples of 4 (then every pointer is
+// 16-byte aligned, the bf16 copy 8-byte); the last len % 4 elements, or the whole range otherwise, go one by one.
+struct Walk {
+  int64_t quads, len;
+  bool vec;
+};
+__device__ __forceinline__ Walk walk_of(const Ranges& r, int y) {
+  const bool vec = ((r.goff[y] | r.coff[y]) & 3) == 0;
+  return Walk{vec ? r.len[y] >> 2 : 0, r.len[y], vec};
+}
+
+// ------------------------------------------------------------------------------------------------ sum of g^2
+__global__ void __launch_bounds__(kThreads) k_sumsq(const float* __restrict__ g, Ranges r, float grad_scale,
+                                                    double* __restrict__ partial) {
+  const int y = blockIdx.y;
+  const Walk wk = walk_of(r, y);
+  const float* gp = g + r.goff[y];
+  double s = 0.0;
+  const int64_t stride = int64_t(gridDim.x) * kThreads, i0 = int64_t(blockIdx.x) * kThreads + threadIdx.x;
+  for (int64_t q = i0; q < wk.quads; q += stride) {
+    const float4 v = reinterpret_cast<const float4*>(gp)[q];
+    s += sq(mul(v.x, grad_scale)) + sq(mul(v.y, grad_scale)) + sq(mul(v.z, grad_scale)) + sq(mul(v.w, grad_scale));
+  }
+  for (int64_t i = wk.quads * 4 + i0; i < wk.len; i += stride) s += sq(mul(gp[i], grad_scale));
+  s = block_sum(s);
+  if (threadIdx.x == 0) partial[int64_t(y) * gridDim.x + blockIdx.x] = s;
+}
+
+// out[j] (+)= sum_i partial[i * width + j], one block, fixed order
+__global__ void __launch_bounds__(kThreads) k_sum_partials(const double* __restrict__ partial, int n, int width,
+                                                           double* __restrict__ out, int accumulate) {
+  for (int j = 0; j < width; ++j) {
+    double s = 0.0;
+    for (int i = threadIdx.x; i < n; i += kThreads) s += partial[int64_t(i) * width + j];
+    s = block_sum(s);
+    if (threadIdx.x == 0) out[j] = accumulate ? out[j] + s : s;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ pass 1
+__global__ void __launch_bounds__(kThreads) k_adamh_moments(Ranges r, const float* __restrict__ g,
+                                                            const float* __restrict__ p, float* __restrict__ mu,
+                                                            float* __restrict__ nu, Hyper h,
+                                                            const double* __restrict__ scal,
+                                                            double* __restrict__ partial) {
+  const int y = blockIdx.y;
+  const Walk wk = walk_of(r, y);
+  const Clip cl = clip_of(h, scal);
+  const float* gp = g + r.goff[y];
+  const float* pp = p + r.coff[y];
+  float* mp = mu + r.coff[y];
+  float* vp = nu + r.coff[y];
+  double spp = 0.0, saa = 0.0, spa = 0.0;
+  auto elem = [&](float gv, float pv, float& m, float& v) {
+    const float gi = clipped(gv, h, cl);
+    m = add(mul(h.one_minus_b1, gi), mul(h.b1, m));
+    v = add(mul(h.one_minus_b2, mul(gi, gi)), mul(h.b2, v));
+    const float a = adam_dir(m, v, h);
+    spp += sq(pv);
+    saa += sq(a);
+    spa = fma(static_cast<double>(pv), static_cast<double>(a), spa);
+  };
+  const int64_t stride = int64_t(gridDim.x) * kThreads, i0 = int64_t(blockIdx.x) * kThreads + threadIdx.x;
+  for (int64_t q = i0; q < wk.quads; q += stride) {
+    const float4 G = reinterpret_cast<const float4*>(gp)[q], P = reinterpret_cast<const float4*>(pp)[q];
+    float4 M = reinterpret_cast<const float4*>(mp)[q], V = reinterpret_cast<const float4*>(vp)[q];
+    elem(G.x, P.x, M.x, V.x);
+    elem(G.y, P.y, M.y, V.y);
+    elem(G.z, P.z, M.z, V.z);
+    elem(G.w, P.w, M.w, V.w);
+    reinterpret_cast<float4*>(mp)[q] = M;
+    reinterpret_cast<float4*>(vp)[q] = V;
+  }
+  for (int64_t i = wk.quads * 4 + i0; i < wk.len; i += stride) {
+    float m = mp[i], v = vp[i];
+    elem(gp[i], pp[i], m, v);
+    mp[i] = m;
+    vp[i] = v;
+  }
+  spp = block_sum(spp);
+  saa = block_sum(saa);
+  spa = block_sum(spa);
+  if (threadIdx.x == 0) {
+    double* o = partial + (int64_t(y) * gridDim.x + blockIdx.x) * 3;
+    o[0] = spp, o[1] = saa, o[2] = spa;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ pass 2 (apply)
+__global__ void __launch_bounds__(kThreads) k_adamh_apply(Ranges r, float* __restrict__ p,
+                                                          const float* __restrict__ mu, const float* __restrict__ nu,
+                                                          __nv_bfloat16* __restrict__ w16, Hyper h,
+                                                          const double* __restrict__ scal) {
+  const int y = blockIdx.y;
+  const Walk wk = walk_of(r, y);
+  // the tensor's norms, from the sums over every rank's ranges
+  const float n = norm_of(scal[kSumPP]);
+  const float m_floor = fmax_nan(norm_of(scal[kSumAA]), 1e-10f);
+  const double c = static_cast<double>(h.eta) * static_cast<double>(n) / static_cast<double>(m_floor);
+  const double ww = scal[kSumPP] - 2.0 * c * scal[kSumPA] + c * c * scal[kSumAA];
+  const float nw = norm_of(ww);
+  float* pp = p + r.coff[y];
+  const float* mp = mu + r.coff[y];
+  const float* vp = nu + r.coff[y];
+  __nv_bfloat16* wp = w16 ? w16 + r.goff[y] : nullptr;
+  auto elem = [&](float pv, float m, float v) {
+    const float a = adam_dir(m, v, h);
+    const float w = sub(pv, dvd(mul(mul(h.eta, a), n), m_floor));
+    const float u = sub(mul(dvd(w, nw), n), pv);
+    return add(pv, u);                                   // p + (target - p), as the reference applies updates
+  };
+  const int64_t stride = int64_t(gridDim.x) * kThreads, i0 = int64_t(blockIdx.x) * kThreads + threadIdx.x;
+  for (int64_t q = i0; q < wk.quads; q += stride) {
+    float4 P = reinterpret_cast<const float4*>(pp)[q];
+    const float4 M = reinterpret_cast<const float4*>(mp)[q], V = reinterpret_cast<const float4*>(vp)[q];
+    P.x = elem(P.x, M.x, V.x);
+    P.y = elem(P.y, M.y, V.y);
+    P.z = elem(P.z, M.z, V.z);
+    P.w = elem(P.w, M.w, V.w);
+    reinterpret_cast<float4*>(pp)[q] = P;
+    if (wp) {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(P.x, P.y), hi = __floats2bfloat162_rn(P.z, P.w);
+      uint2 o;
+      o.x = *reinterpret_cast<const uint32_t*>(&lo);
+      o.y = *reinterpret_cast<const uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(wp)[q] = o;
+    }
+  }
+  for (int64_t i = wk.quads * 4 + i0; i < wk.len; i += stride) {
+    const float pv = elem(pp[i], mp[i], vp[i]);
+    pp[i] = pv;
+    if (wp) wp[i] = __float2bfloat16_rn(pv);
+  }
+}
+
+// master copy from the bf16 replica: p[compact] = f32(w16[global]) over the owned ranges
+__global__ void __launch_bounds__(kThreads) k_master_from_bf16(Ranges r, const __nv_bfloat16* __restrict__ w16,
+                                                               float* __restrict__ p) {
+  const int y = blockIdx.y;
+  const int64_t stride = int64_t(gridDim.x) * kThreads, i0 = int64_t(blockIdx.x) * kThreads + threadIdx.x;
+  for (int64_t i = i0; i < r.len[y]; i += stride) p[r.coff[y] + i] = __bfloat162float(w16[r.goff[y] + i]);
+}
+
+int blocks_for(const Ranges& r) {
+  int64_t longest = 1;
+  for (int i = 0; i < r.n; ++i) longest = longest > r.len[i] ? longest : r.len[i];
+  const int64_t want = (longest / 4 + kThreads * 4 - 1) / (kThreads * 4);          // about 4 quads per thread
+  const int64_t cap = std::max<int64_t>(1, int64_t(kMaxBlocksTotal) / std::max(1, r.n));
+  return int(std::max<int64_t>(1, std::min(want, cap)));
+}
+
+}  // namespace
+
+int partial_blocks(const Ranges& r) { return blocks_for(r) * r.n; }
+
+void launch_sumsq(const float* g, const Ranges& r, float grad_scale, double* partial, double* out, bool accumulate,
+                  cudaStream_t st) {
+  if (r.n <= 0) return;
+  const int bx = blocks_for(r);
+  k_sumsq<<<dim3(bx, r.n), kThreads, 0, st>>>(g, r, grad_scale, partial);
+  NM_CUDA(cudaGetLastError());
+  k_sum_partials<<<1, kThreads, 0, st>>>(partial, bx * r.n, 1, out, accumulate ? 1 : 0);
+  NM_CUDA(cudaGetLastError());
+}
+
+void launch_moments(const Ranges& r, const float* g, const float* p, float* mu, float* nu, const Hyper& h,
+                    double* scal, double* partial, cudaStream_t st) {
+  if (r.n <= 0) return;
+  const int bx = blocks_for(r);
+  k_adamh_moments<<<dim3(bx, r.n), kThreads, 0, st>>>(r, g, p, mu, nu, h, scal, partial);
+  NM_CUDA(cudaGetLastError());
+  k_sum_partials<<<1, kThreads, 0, st>>>(partial, bx * r.n, 3, scal + kSumPP, 0);
+  NM_CUDA(cudaGetLastError());
+}
+
+void launch_apply(const Ranges& r, float* p, const float* mu, const float* nu, void* w16, const Hyper& h,
+                  const double* scal, cudaStream_t st) {
+  if (r.n <= 0) return;
+  k_adamh_apply<<<dim3(blocks_for(r), r.n), kThreads, 0, st>>>(r, p, mu, nu, static_cast<__nv_bfloat16*>(w16), h, scal);
+  NM_CUDA(cudaGetLastError());
+}
+
+void launch_master_from_bf16(const Ranges& r, const void* w16, float* p, cudaStream_t st) {
+  if (r.n <= 0) return;
+  k_master_from_bf16<<<dim3(blocks_for(r), r.n), kThreads, 0, st>>>(r, static_cast<const __nv_bfloat16*>(w16), p);
+  NM_CUDA(cudaGetLastError());
+}
+
+}  // namespace nm::opt

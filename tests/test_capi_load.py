@@ -24,7 +24,7 @@ def lib():
 
 def declared_symbols():
     names = set()
-    for h in ("capi.h", "capi_ce.h", "capi_ew.h"):
+    for h in ("capi.h", "capi_ce.h", "capi_ew.h", "capi_opt.h"):
         text = open(os.path.join(ROOT, "include", "marincpp", h)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
         names |= set(re.findall(r"\b(nm_[a-z0-9_]+)\s*\(", text))

@@ -50,3 +50,19 @@ def test_bucketed_dw_allreduce_matches_single_gpu():
         pytest.skip("needs 2 GPUs")
     out = _launch("nccl", 2, 29612)
     assert "reduce dtype 0" in out and "reduce dtype 1" in out
+
+
+@pytest.mark.gpu
+def test_zero1_adamh_on_two_gpus():
+    """Reduce-scatter to owners, AdamH on owned element ranges, all-gather of the bf16 replica, on 2 GPUs over NCCL,
+    against the single-rank oracle (tests/adamh_rank_worker.py)."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    worker = os.path.join(ROOT, "tests", "adamh_rank_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29622", worker, "--backend", "nccl"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="2",
+                                                                                   NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "nccl world 2" in r.stdout
