@@ -110,3 +110,48 @@ def test_against_the_reference_training_path_and_shared_bits(ref):
     ref.nm_ce_set_backends(0, 0, -1)
     want = O.chunk_loss_tree(theirs[0].cpu().numpy(), wt, chunk)
     assert theirs[4].cpu().numpy().tobytes() == want.tobytes(), "the oracle's loss tree is the reference kernel's, to the bit"
+
+
+# ------------------------------------------------------------------------------------------------ AdamH of the head
+REF_OPT = os.path.join(ROOT, "oracle", "_ref", "libref_optim.so")
+
+
+@pytest.mark.parametrize("shape,t,clip", [((2048, 512), 1, False), ((1000, 264), 7, True), ((8192, 2048), 300, True)])
+def test_adamh_update_against_the_reference_library(shape, t, clip):
+    """nm_adamh_update of this library against the reference's own implementation of the same entry point
+    (src/optim/capi_optim.cpp:202-219 -> engine -> optk_adam.cu), built unmodified for sm_100a. Moments must be
+    bit-equal (element arithmetic in the same order); the parameters agree to 1e-6, the bar the reference holds between
+    its own scalar and float4 paths, whose norms sum in different orders (tests/s6/test_engine.cpp:538-590)."""
+    if not os.path.exists(REF_OPT):
+        pytest.skip("oracle/_ref/libref_optim.so was not built (make -C oracle _ref/libref_optim.so)")
+    import ctypes
+    import time
+    from gpu_common import lib, nmce
+    rdll = ctypes.CDLL(REF_OPT)
+    rdll.nm_adamh_update.restype, rdll.nm_adamh_update.argtypes = nmce.SIGS["nm_adamh_update"]
+    rdll.nm_last_error.restype = ctypes.c_char_p
+    rng = np.random.default_rng(shape[0] + t)
+    p = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+    g = (rng.standard_normal(shape) * 1e-3).astype(np.float32)
+    mu = (rng.standard_normal(shape) * 1e-3).astype(np.float32)
+    nu = ((rng.standard_normal(shape) * 1e-3) ** 2).astype(np.float32)
+    gn = float(np.sqrt(np.float32(np.sum((g * g).astype(np.float64)))))
+    max_norm = 0.5 * gn if clip else 1.0
+    out = {}
+    for name, fn in (("ours", lib().raw("nm_adamh_update")), ("ref", rdll.nm_adamh_update)):
+        P, G, M, V = (torch.from_numpy(a.copy()).cuda() for a in (p, g, mu, nu))
+        P16 = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        rc = fn(nmce.ptr(P), nmce.ptr(P16), nmce.ptr(G), nmce.ptr(M), nmce.ptr(V), shape[0], shape[1], t, 0.02, 0.9,
+                0.98, 1e-20, gn, int(clip), max_norm, None, None, None, 0, None)
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3
+        assert rc == 0, (name, rdll.nm_last_error())
+        out[name] = (P, M, V, P16, ms)
+    (P, M, V, P16, ms), (RP, RM, RV, RP16, rms) = out["ours"], out["ref"]
+    assert torch.equal(M, RM) and torch.equal(V, RV), "moments differ from the reference's bits"
+    r = float((P.double() - RP.double()).norm() / RP.double().norm())
+    assert r <= 1e-6, f"p rel {r:.3e}"
+    assert int((P16 != RP16).sum()) <= 1e-4 * P16.numel()       # an f32 difference of 1 ulp can flip a bf16 tie
+    print(f"AdamH {shape} t={t}: p rel vs reference {r:.2e}; host wall of one call {ms:.2f} ms vs reference {rms:.2f} ms")
