@@ -168,7 +168,7 @@ def reference_arm_gpu(args, cfg):
     dev = torch.device("cuda", 0)
     T, D, V = cfg["T"], cfg["D"], cfg["V"]
     R = cfg["readouts"]
-    chunk = min(args.chunk, T)
+    chunk = min(args.chunk or 16384, T)          # the reference's callers pass 16384 (tests/s5/bench_ce.py)
     X, W, Y, WT = make_inputs(torch, cfg, 0, dev)
     gs = (1.0 / WT.sum()).float().reshape(1) / R
     dx = torch.empty_like(X)
@@ -266,10 +266,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--chunk", type=int, default=16384)
+    ap.add_argument("--chunk", type=int, default=0, help="chunk rows; 0 = nm_ce_suggest_chunk_rows (128 x SM count)")
     ap.add_argument("--buckets", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (small cases for profiling)")
-    ap.add_argument("--cta-pair", default="", help="three digits (logits, dX, dW): 1 = a CTA pair per tile, e.g. 011")
+    ap.add_argument("--cta-pair", default="", help="three digits (logits, dX, dW): 1 = a CTA pair per tile, 0 = one CTA, e.g. 011; default: chosen per launch")
     ap.add_argument("--zero1", action="store_true",
                     help="reduce dW to its owners (reduce-scatter), AdamH on owned elements and all-gather of the bf16 "
                          "head inside every step, instead of the dW all-reduce (the optimizer then is in the timing)")
@@ -306,7 +306,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     T, D, V, L = cfg["T"], cfg["D"], cfg["V"], cfg["z_loss"]
     R = cfg["readouts"]
-    chunk = min(args.chunk, T)
+    chunk = min(args.chunk or int(lib.nm_ce_suggest_chunk_rows(T)), T)
     n_chunks = (T + chunk - 1) // chunk
 
     X, W, Y, WT = make_inputs(torch, cfg, rank, dev)

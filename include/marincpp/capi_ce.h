@@ -66,9 +66,17 @@ int nm_ce_profile_read(double* ms_host /*[6]*/, int* launches_host /*[6]*/);
  * same barrier with a long limit must leave through that flag (*saw_abort = 1). The kernel then returns normally. */
 int nm_ce_test_wait_timeout(uint32_t* status, int64_t limit_cycles, int* saw_abort, void* stream);
 
+/* A chunk size for a call of T rows on the current device: min(T, 128 x SM count) rows (18944 on a B200). With it the
+ * tile counts of the logits and dX kernels of every full chunk are whole multiples of the SM count (one persistent CTA
+ * per SM, 128-row tiles), so no wave of tiles runs part-filled; 16384 leaves the dX kernel at 86 % of its last wave
+ * for hidden sizes up to 1024. Returns 0 without a device. No counterpart in the reference (its callers pass 16384). */
+int nm_ce_suggest_chunk_rows(int64_t T);
+
 /* How many CTAs work on one accumulator tile in the logits, dX and dW contractions: 0 = one CTA per 128 x 256 tile,
  * non-zero = a pair of CTAs on one TPC per 256 x 256 tile (tcgen05 cta_group::2; the B operand is staged once per
- * pair). Results are bit-identical between the two forms. Process-wide; call it while no CE call is in flight. No
+ * pair), negative = chosen per launch (the default: pairs for the dX and dW contractions of calls with hidden size up
+ * to 512 and at most 16384 rows per chunk, where they were measured to pay; one CTA per tile otherwise). Results are
+ * bit-identical between the two forms. Process-wide; call it while no CE call is in flight. No
  * counterpart in the reference (its nm_ce_set_backends chooses between its own kernels and cuBLASLt). */
 int nm_ce_set_cta_pair(int logits, int dgrad, int wgrad);
 

@@ -173,6 +173,15 @@ int nm_ce_test_wait_timeout(uint32_t* status, int64_t limit_cycles, int* saw_abo
       [&] { nm::ce::launch_wait_timeout_probe(status, static_cast<long long>(limit_cycles), saw_abort, S(stream)); });
 }
 
+int nm_ce_suggest_chunk_rows(int64_t T) {
+  int rows = 0;
+  const int rc = nm::capi_call([&] {
+    const int64_t full = int64_t(128) * nm::ce::sm_count();
+    rows = int(T < full ? (T > 0 ? T : 1) : full);
+  });
+  return rc == NM_OK ? rows : 0;
+}
+
 int nm_ce_set_cta_pair(int logits, int dgrad, int wgrad) {
   return nm::capi_call([&] { nm::ce::set_cta_pair(logits, dgrad, wgrad); });
 }

@@ -687,15 +687,22 @@ void launch(int ncta, const CUtensorMap& ta, const CUtensorMap& tb, const CUtens
   else launch_n<EPI, A_MN, B_MN, 1>(ta, tb, tc, p, st, sm_reserve);
 }
 
-// CTAs per tile for the three contractions (1, or 2 = pair mode), per process
-int g_ncta[3] = {1, 1, 1};
+// CTAs per tile for the three contractions: 1, 2 (pair mode) or 0 = chosen per launch. Pairs finish a tile in fewer
+// cycles but draw more power, and on the power-capped large shapes the kernels around them lose what the paired
+// kernel gains; measured, they pay for the dX and dW contractions of short, narrow calls (hidden size up to 512, at
+// most 16384 rows per chunk: the per-layer readouts), 2.8 % of that step.
+int g_ncta[3] = {0, 0, 0};
+int ncta_for(int which, int rows, int D) {
+  if (g_ncta[which] != 0) return g_ncta[which];
+  return (which != 0 && D <= 512 && rows <= 16384) ? 2 : 1;
+}
 
 }  // namespace
 
 void launch_logits(const LogitsArgs& a, cudaStream_t st) {
   if (a.rows <= 0) return;
   GemmParams p{};
-  const int ncta = g_ncta[0], bmt = BM * ncta;
+  const int ncta = ncta_for(0, a.rows, a.D), bmt = BM * ncta;
   p.M = a.rows; p.N = a.V; p.K = a.D; p.m_off = 0;
   p.num_m = (a.rows + bmt - 1) / bmt; p.num_n = (a.V + BN - 1) / BN; p.m_inner = 1;
   // rows are walked in groups whose x tiles (group x 128 x D bf16) take about 16 MiB of L2: x is then read from HBM
@@ -714,7 +721,7 @@ void launch_logits(const LogitsArgs& a, cudaStream_t st) {
 void launch_dgrad(const DgradArgs& a, cudaStream_t st) {
   if (a.rows <= 0) return;
   GemmParams p{};
-  const int ncta = g_ncta[1], bmt = BM * ncta;
+  const int ncta = ncta_for(1, a.rows, a.D), bmt = BM * ncta;
   p.M = a.rows; p.N = a.D; p.K = a.V; p.m_off = 0;
   p.num_m = (a.rows + bmt - 1) / bmt; p.num_n = (a.D + BN - 1) / BN; p.m_inner = 0;
   p.m_group = 1;
@@ -731,7 +738,7 @@ void launch_wgrad(const WgradArgs& a, cudaStream_t st) {
   NM_REQUIRE(a.v0 % BM == 0 && (a.v1 % BM == 0 || a.v1 == a.V) && a.v1 <= a.V,
              "fused CE: a dW vocabulary range must start and end on multiples of 128 (or end at V)");
   GemmParams p{};
-  const int ncta = g_ncta[2], bmt = BM * ncta;
+  const int ncta = ncta_for(2, a.rows, a.D), bmt = BM * ncta;
   p.M = a.v1 - a.v0; p.N = a.D; p.K = a.rows; p.m_off = a.v0;
   p.num_m = (p.M + bmt - 1) / bmt; p.num_n = (a.D + BN - 1) / BN; p.m_inner = 0;
   p.m_group = 1;
@@ -744,7 +751,8 @@ void launch_wgrad(const WgradArgs& a, cudaStream_t st) {
 }
 
 void set_cta_pair(int logits, int dgrad, int wgrad) {
-  g_ncta[0] = logits ? 2 : 1; g_ncta[1] = dgrad ? 2 : 1; g_ncta[2] = wgrad ? 2 : 1;
+  const int v[3] = {logits, dgrad, wgrad};
+  for (int i = 0; i < 3; ++i) g_ncta[i] = v[i] < 0 ? 0 : (v[i] ? 2 : 1);
 }
 
 void launch_wait_timeout_probe(uint32_t* status, long long limit_cycles, int* saw_abort, cudaStream_t st) {

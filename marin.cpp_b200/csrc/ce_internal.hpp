@@ -98,7 +98,8 @@ void launch_wgrad(const WgradArgs& a, cudaStream_t st);
 void launch_wait_timeout_probe(uint32_t* status, long long limit_cycles, int* saw_abort, cudaStream_t st);
 
 // CTAs per accumulator tile of the three contractions: 0 = one CTA per 128 x 256 tile, 1 = a pair of CTAs (cluster of
-// two, one UMMA of M = 256 over both) per 256 x 256 tile. Process-wide; not to be changed while a call is in flight.
+// two, one UMMA of M = 256 over both) per 256 x 256 tile, negative = chosen per launch (the default). Process-wide;
+// not to be changed while a call is in flight.
 void set_cta_pair(int logits, int dgrad, int wgrad);
 
 // unit-test entry: C f32 [M, N] = A B^T in the three operand layouts (kind 0 K/K, 1 K/MN, 2 MN/MN; + 4: CTA pairs)
