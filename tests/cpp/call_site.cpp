@@ -1,6 +1,8 @@
 // The reference trainer's call site (src/model/baseline.cpp:366-373) written against this repository's headers and
 // linked against its static archive: builds CeShape / CeArgs the same way, calls nm::ce_workspace_bytes and
-// nm::fused_linear_ce, then sums the per-chunk losses. Prints "loss_sum <value> dw_abs <value> dx_abs <value>".
+// nm::fused_linear_ce, then sums the per-chunk losses. Prints "loss_sum <value> dw_abs <value> dx_abs <value>". Then the
+// optimizer site for the head: nm::HeadAdamH (one rank owns the whole tensor) on the dW just produced, printing
+// "p_abs <value> w16_abs <value>".
 // Inputs: a fixed integer-hash pattern (no RNG library), so a Python test can rebuild them and compare.
 #include <cuda_runtime.h>
 
@@ -11,6 +13,7 @@
 
 #include "marincpp/core.hpp"
 #include "marincpp/kernels/cross_entropy.hpp"
+#include "marincpp/kernels/head_optim.hpp"
 
 namespace nm { class GemmCache {}; }   // the CE path ignores it; the trainer passes its planner
 
@@ -81,5 +84,31 @@ int main() {
   for (float v : hdw) aw += std::fabs(v);
   for (const bf16_t& v : hdx) ax += std::fabs(bf16_bits_to_f32(v.bits));
   std::printf("loss_sum %.9g dw_abs %.9g dx_abs %.9g\n", ls * hgs, aw, ax);
+
+  // the head's update from that gradient: master copy from the bf16 replica, zero moments, first update
+  float *p32, *mu, *nu;
+  const size_t n = size_t(V) * D;
+  CK(cudaMalloc(&p32, n * 4)); CK(cudaMalloc(&mu, n * 4)); CK(cudaMalloc(&nu, n * 4));
+  CK(cudaMemset(mu, 0, n * 4)); CK(cudaMemset(nu, 0, n * 4));
+  try {
+    HeadAdamH opt(V, D, nullptr);
+    if (opt.owned_elems() != int64_t(n)) { std::printf("owned_elems mismatch\n"); return 4; }
+    opt.init_master(static_cast<const bf16_t*>(w), p32, s);
+    AdamHStep st;
+    st.t = 1, st.eta = 0.02f, st.b1 = 0.9f, st.b2 = 0.98f, st.eps = 1e-20f, st.max_grad_norm = 1.0f, st.grad_scale = 1.0f;
+    opt.step(st, dw, p32, mu, nu, static_cast<bf16_t*>(w), s);
+    CK(cudaStreamSynchronize(s));
+  } catch (const Fatal& e) {
+    std::printf("HeadAdamH threw: %s\n", e.what());
+    return 5;
+  }
+  std::vector<float> hpn(n);
+  std::vector<bf16_t> hw2(n);
+  CK(cudaMemcpy(hpn.data(), p32, n * 4, cudaMemcpyDeviceToHost));
+  CK(cudaMemcpy(hw2.data(), w, n * 2, cudaMemcpyDeviceToHost));
+  double ap = 0, a16 = 0;
+  for (float v : hpn) ap += std::fabs(v);
+  for (const bf16_t& v : hw2) a16 += std::fabs(bf16_bits_to_f32(v.bits));
+  std::printf("p_abs %.9g w16_abs %.9g\n", ap, a16);
   return 0;
 }

@@ -24,6 +24,7 @@ def test_call_site_compiles_and_links():
     assert os.path.exists(exe) and os.access(exe, os.X_OK)
     syms = subprocess.check_output(["nm", "-C", "--defined-only", exe], text=True)
     assert "nm::fused_linear_ce" in syms and "nm::ce_workspace_bytes" in syms
+    assert "nm::HeadAdamH::step" in syms
 
 
 def _hash_unit(i, salt):
@@ -62,3 +63,17 @@ def test_call_site_runs_and_matches_the_c_abi():
     assert abs(float(lp.double().sum()) * float(gs) - loss_sum) <= 1e-6 * abs(loss_sum)
     assert abs(float(dw.double().abs().sum()) - dw_abs) <= 1e-5 * dw_abs
     assert abs(float(dx.double().abs().sum()) - dx_abs) <= 1e-5 * dx_abs
+    # the optimizer site: nm::HeadAdamH in the C++ program against nm_adamh_update (C ABI) on the same gradient
+    m2 = re.search(r"p_abs (\S+) w16_abs (\S+)", out)
+    assert m2, out
+    p_abs, w16_abs = (float(v) for v in m2.groups())
+    lib = nmce.Lib()
+    P = W.float().contiguous()
+    MU, NU = torch.zeros_like(P), torch.zeros_like(P)
+    P16 = torch.empty_like(W)
+    gn = float(np.sqrt(np.float32(float((dw.float() * dw.float()).double().sum()))))
+    lib.nm_adamh_update(nmce.ptr(P), nmce.ptr(P16), nmce.ptr(dw), nmce.ptr(MU), nmce.ptr(NU), V, D, 1, 0.02, 0.9, 0.98,
+                        1e-20, gn, int(not gn < 1.0), 1.0, None, None, None, 0, None)
+    torch.cuda.synchronize()
+    assert abs(float(P.double().abs().sum()) - p_abs) <= 1e-6 * p_abs
+    assert abs(float(P16.double().abs().sum()) - w16_abs) <= 1e-5 * w16_abs
