@@ -85,3 +85,14 @@ def test_no_device_is_a_loud_error(lib):
     with pytest.raises(nmce.NmError) as e:
         lib.nm_ce_grad_scale(ctypes.addressof(buf), 64, 1.0, ctypes.addressof(buf), None)
     assert e.value.status == 2
+    # the chunk-size helper needs the SM count: 0 and a message without a device
+    assert lib.nm_ce_suggest_chunk_rows(131072) == 0 and lib.nm_last_error() != b""
+    # the optimizer entry points fail the same way: argument checks first, then the device
+    with pytest.raises(nmce.NmError) as e:
+        lib.nm_adamh_update(ctypes.addressof(buf), None, ctypes.addressof(buf), ctypes.addressof(buf),
+                            ctypes.addressof(buf), 8, 8, 0, 0.02, 0.9, 0.98, 1e-20, 0.0, 0, 1.0, None, None, None, 0, None)
+    assert e.value.status == 1 and "update count" in str(e.value)
+    with pytest.raises(nmce.NmError) as e:
+        lib.nm_adamh_update(ctypes.addressof(buf), None, ctypes.addressof(buf), ctypes.addressof(buf),
+                            ctypes.addressof(buf), 8, 8, 1, 0.02, 0.9, 0.98, 1e-20, 0.0, 0, 1.0, None, None, None, 0, None)
+    assert e.value.status == 2

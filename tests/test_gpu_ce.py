@@ -454,3 +454,12 @@ def test_two_devices_same_bits():
             outs.append([t.cpu() for t in (loss, lse, dx, dw)])
     for a, b in zip(*outs):
         assert same_bits(a, b)
+
+
+def test_suggested_chunk_rows():
+    """nm_ce_suggest_chunk_rows: min(T, 128 x SM count), so that the tiles of a full chunk fill whole waves."""
+    from gpu_common import lib
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert lib().nm_ce_suggest_chunk_rows(131072) == min(131072, 128 * sms)
+    assert lib().nm_ce_suggest_chunk_rows(1000) == 1000
+    assert lib().nm_ce_suggest_chunk_rows(0) == 1
