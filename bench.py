@@ -550,11 +550,10 @@ def main():
     dom_launch_ms = prof_ms[names.index(dom)] / max(1, prof_n[names.index(dom)])
     dom_flop_launch = 2.0 * R * T * D * V * args.steps / max(1, prof_n[names.index(dom)])
     achieved = dom_flop_launch / (dom_launch_ms * 1e-3) / 1e12
-    # DRAM bytes per launch of each tcgen05 kernel at 16384 rows x 2048 x 128256, from one ncu capture of this bench
-    # (dram__bytes_read.sum + dram__bytes_write.sum; summary under profiles/); unknown for other shapes
-    traffic = None
-    if (D, V, chunk) == (2048, 128256, 16384):
-        traffic = {"logits": 6.40e9, "dw": 10.07e9, "dx": 8.04e9}[dom]
+    # DRAM bytes per launch of each tcgen05 kernel at hidden 2048 x vocab 128256, from ncu captures of this bench
+    # (dram__bytes_read.sum + dram__bytes_write.sum; summaries under profiles/); unknown for other shapes
+    traffic = {(2048, 128256, 18944): {"logits": 7.60e9, "dw": 11.34e9, "dx": 9.26e9},
+               (2048, 128256, 16384): {"logits": 6.40e9, "dw": 10.07e9, "dx": 8.04e9}}.get((D, V, chunk), {}).get(dom)
     out = {
         "metric": "fused_ce_fwd_bwd_tokens_per_s", "value": tokens / (ms_total * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
