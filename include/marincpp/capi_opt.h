@@ -20,6 +20,14 @@ int nm_adamh_update(float* p, void* p16, const float* g, float* mu, float* nu, i
                     const int32_t* block_of_row, const float* block_lr_mult, const uint8_t* block_frozen,
                     int n_blocks, void* stream);
 
+/* reference include/marincpp/capi.h:111-114: one plain Adam update of one tensor, p += (-adam_lr) a with the same
+ * moments, bias corrections and clip as above and no projection (the rule of the final norm's gain, whose gradient the
+ * readout entry point produces). Row blocks: as above, not supported. */
+int nm_adam_update(float* p, void* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
+                   float adam_lr, float b1, float b2, float eps, float clip_gn, int clip, float max_norm,
+                   const int32_t* block_of_row, const float* block_lr_mult, const uint8_t* block_frozen,
+                   int n_blocks, void* stream);
+
 /* ---- ZeRO-1 form (the design of the reference's include/marincpp/comm.hpp:22-71; no C entry points there) -------- */
 
 /* nm_grad_reducer_create (capi_ce.h) with a reduction to owners: every bucket is reduce-scattered (f32), rank r keeps

@@ -26,6 +26,10 @@ struct AdamHStep {
   float b1 = 0.9f, b2 = 0.98f, eps = 1e-20f;
   float max_grad_norm = 1.0f;    // <= 0: no clip
   float grad_scale = 1.0f;       // the gradient is multiplied by this first (1 / microbatches)
+  // bias corrections 1 - b^t from the trainer's schedule tables (the reference computes them with XLA's f32 pow,
+  // docs/spec/optim.md:322-335); 0 = computed here as f32(1 - pow(f32(b), t)) with the power taken in f64, which can
+  // differ from that table by one ulp of b^t (AdamH divides the factor out again, plain Adam does not)
+  float bc1 = 0.f, bc2 = 0.f;
 };
 
 class HeadAdamH {
@@ -68,5 +72,10 @@ class HeadAdamH {
 // whole [rows, cols] tensor on one GPU, clip state given by the caller. Row blocks (block_of_row) are not supported.
 void adamh_update(float* p, bf16_t* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
                   float eta, float b1, float b2, float eps, float clip_gn, bool clip, float max_norm, cudaStream_t st);
+
+// The reference's one-tensor Adam entry point (include/marincpp/capi.h:111-114): p += (-adam_lr) a, no projection; for
+// the tensors beside the head on this path (the final norm's gain). Row blocks are not supported.
+void adam_update(float* p, bf16_t* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
+                 float adam_lr, float b1, float b2, float eps, float clip_gn, bool clip, float max_norm, cudaStream_t st);
 
 }  // namespace nm

@@ -195,6 +195,56 @@ __global__ void __launch_bounds__(kThreads) k_adamh_apply(Ranges r, float* __res
   }
 }
 
+// ------------------------------------------------------------------------------------------------ plain Adam
+// The reference's Adam rule (optk_adam.cu:38-82) for the tensors beside the head (the final norm's gain): moments as
+// above, u = ((-lr) a), p = p + u; no projection, so one pass.
+__global__ void __launch_bounds__(kThreads) k_adam(Ranges r, const float* __restrict__ g, float* __restrict__ p,
+                                                   float* __restrict__ mu, float* __restrict__ nu,
+                                                   __nv_bfloat16* __restrict__ w16, Hyper h,
+                                                   const double* __restrict__ scal) {
+  const int y = blockIdx.y;
+  const Walk wk = walk_of(r, y);
+  const Clip cl = clip_of(h, scal);
+  const float neg_lr = -h.eta;
+  const float* gp = g + r.goff[y];
+  float* pp = p + r.coff[y];
+  float* mp = mu + r.coff[y];
+  float* vp = nu + r.coff[y];
+  __nv_bfloat16* wp = w16 ? w16 + r.goff[y] : nullptr;
+  auto elem = [&](float gv, float& pv, float& m, float& v) {
+    const float gi = clipped(gv, h, cl);
+    m = add(mul(h.one_minus_b1, gi), mul(h.b1, m));
+    v = add(mul(h.one_minus_b2, mul(gi, gi)), mul(h.b2, v));
+    pv = add(pv, mul(neg_lr, adam_dir(m, v, h)));
+  };
+  const int64_t stride = int64_t(gridDim.x) * kThreads, i0 = int64_t(blockIdx.x) * kThreads + threadIdx.x;
+  for (int64_t q = i0; q < wk.quads; q += stride) {
+    const float4 G = reinterpret_cast<const float4*>(gp)[q];
+    float4 P = reinterpret_cast<const float4*>(pp)[q], M = reinterpret_cast<const float4*>(mp)[q],
+           V = reinterpret_cast<const float4*>(vp)[q];
+    elem(G.x, P.x, M.x, V.x);
+    elem(G.y, P.y, M.y, V.y);
+    elem(G.z, P.z, M.z, V.z);
+    elem(G.w, P.w, M.w, V.w);
+    reinterpret_cast<float4*>(pp)[q] = P;
+    reinterpret_cast<float4*>(mp)[q] = M;
+    reinterpret_cast<float4*>(vp)[q] = V;
+    if (wp) {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(P.x, P.y), hi = __floats2bfloat162_rn(P.z, P.w);
+      uint2 o;
+      o.x = *reinterpret_cast<const uint32_t*>(&lo);
+      o.y = *reinterpret_cast<const uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(wp)[q] = o;
+    }
+  }
+  for (int64_t i = wk.quads * 4 + i0; i < wk.len; i += stride) {
+    float pv = pp[i], m = mp[i], v = vp[i];
+    elem(gp[i], pv, m, v);
+    pp[i] = pv, mp[i] = m, vp[i] = v;
+    if (wp) wp[i] = __float2bfloat16_rn(pv);
+  }
+}
+
 // master copy from the bf16 replica: p[compact] = f32(w16[global]) over the owned ranges
 __global__ void __launch_bounds__(kThreads) k_master_from_bf16(Ranges r, const __nv_bfloat16* __restrict__ w16,
                                                                float* __restrict__ p) {
@@ -239,6 +289,13 @@ void launch_apply(const Ranges& r, float* p, const float* mu, const float* nu, v
                   const double* scal, cudaStream_t st) {
   if (r.n <= 0) return;
   k_adamh_apply<<<dim3(blocks_for(r), r.n), kThreads, 0, st>>>(r, p, mu, nu, static_cast<__nv_bfloat16*>(w16), h, scal);
+  NM_CUDA(cudaGetLastError());
+}
+
+void launch_adam(const Ranges& r, const float* g, float* p, float* mu, float* nu, void* w16, const Hyper& h,
+                 const double* scal, cudaStream_t st) {
+  if (r.n <= 0) return;
+  k_adam<<<dim3(blocks_for(r), r.n), kThreads, 0, st>>>(r, g, p, mu, nu, static_cast<__nv_bfloat16*>(w16), h, scal);
   NM_CUDA(cudaGetLastError());
 }
 

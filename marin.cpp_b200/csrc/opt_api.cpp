@@ -103,6 +103,8 @@ void HeadAdamH::step(const AdamHStep& s, const float* grad, float* p_owned, floa
                      bf16_t* w16, cudaStream_t st) {
   NM_REQUIRE(grad && p_owned && mu_owned && nu_owned, "head adamh: grad, p, mu, nu required");
   opt::Hyper h = make_hyper(s.t, s.eta, s.b1, s.b2, s.eps, s.grad_scale);
+  if (s.bc1 > 0.f) h.bc1 = s.bc1;
+  if (s.bc2 > 0.f) h.bc2 = s.bc2;
   const opt::Ranges& r = impl_->r;
   Comm* comm = reducer_ && reducer_->comm().nranks() > 1 ? &reducer_->comm() : nullptr;
   if (reducer_) reducer_->wait(st);
@@ -155,6 +157,21 @@ void adamh_update(float* p, bf16_t* p16, const float* g, float* mu, float* nu, i
   NM_CUDA(cudaFreeAsync(scratch, st));
 }
 
+void adam_update(float* p, bf16_t* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
+                 float adam_lr, float b1, float b2, float eps, float clip_gn, bool clip, float max_norm, cudaStream_t st) {
+  NM_REQUIRE(p && g && mu && nu, "adam_update: p, g, mu, nu required");
+  NM_REQUIRE(rows > 0 && cols > 0, "adam_update: rows, cols > 0");
+  opt::Hyper h = make_hyper(t, adam_lr, b1, b2, eps, 1.0f);
+  h.clip_mode = 1;
+  h.clip = clip ? 1 : 0;
+  h.clip_gn = clip_gn;
+  h.max_norm = max_norm;
+  opt::Ranges r;
+  r.n = 1;
+  r.goff[0] = 0, r.coff[0] = 0, r.len[0] = rows * cols;
+  opt::launch_adam(r, g, p, mu, nu, p16, h, nullptr, st);
+}
+
 }  // namespace nm
 
 // ------------------------------------------------------------------------------------------------ C ABI
@@ -177,6 +194,18 @@ int nm_adamh_update(float* p, void* p16, const float* g, float* mu, float* nu, i
                "nm_adamh_update: row blocks are not supported by this library (pass NULL, NULL, NULL, 0)");
     nm::adamh_update(p, static_cast<nm::bf16_t*>(p16), g, mu, nu, rows, cols, t, eta, b1, b2, eps, clip_gn, clip != 0,
                      max_norm, S(stream));
+  });
+}
+
+int nm_adam_update(float* p, void* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
+                   float adam_lr, float b1, float b2, float eps, float clip_gn, int clip, float max_norm,
+                   const int32_t* block_of_row, const float* block_lr_mult, const uint8_t* block_frozen, int n_blocks,
+                   void* stream) {
+  return nm::capi_call([&] {
+    NM_REQUIRE(!block_of_row && !block_lr_mult && !block_frozen && n_blocks == 0,
+               "nm_adam_update: row blocks are not supported by this library (pass NULL, NULL, NULL, 0)");
+    nm::adam_update(p, static_cast<nm::bf16_t*>(p16), g, mu, nu, rows, cols, t, adam_lr, b1, b2, eps, clip_gn,
+                    clip != 0, max_norm, S(stream));
   });
 }
 

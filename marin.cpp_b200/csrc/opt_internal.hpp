@@ -41,6 +41,9 @@ void launch_moments(const Ranges& r, const float* g, const float* p, float* mu, 
 // pass 2: p updated in place, bf16(p) written at the global positions of w16 (nullable)
 void launch_apply(const Ranges& r, float* p, const float* mu, const float* nu, void* w16, const Hyper& h,
                   const double* scal, cudaStream_t st);
+// plain Adam in one pass: p += (-eta) a (h.eta is the Adam learning rate); scal is read only with clip_mode 2
+void launch_adam(const Ranges& r, const float* g, float* p, float* mu, float* nu, void* w16, const Hyper& h,
+                 const double* scal, cudaStream_t st);
 void launch_master_from_bf16(const Ranges& r, const void* w16, float* p, cudaStream_t st);
 
 }  // namespace nm::opt

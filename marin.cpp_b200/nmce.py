@@ -58,6 +58,8 @@ SIGS = {
     "nm_grad_reducer_wait": (I32, [VP, VP]),
     "nm_adamh_update": (I32, [VP, VP, VP, VP, VP, I64, I64, I64, F32, F32, F32, F32, F32, I32, F32, VP, VP, VP, I32,
                               VP]),
+    "nm_adam_update": (I32, [VP, VP, VP, VP, VP, I64, I64, I64, F32, F32, F32, F32, F32, I32, F32, VP, VP, VP, I32,
+                             VP]),
     "nm_grad_reducer_create_owners": (I32, [VP, VP, I32, I32, I32, VP]),
     "nm_head_adamh_create": (I32, [I32, I32, VP, VP]),
     "nm_head_adamh_destroy": (I32, [VP]),

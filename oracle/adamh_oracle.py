@@ -77,6 +77,23 @@ def adamh_f32(p, g, mu, nu, t, eta, b1, b2, eps, clip_gn=0.0, clip=False, max_no
     return p2, mu2, nu2, {"n": n, "m": m, "nw": nw, "a": a}
 
 
+def adam_f32(p, g, mu, nu, t, lr, b1, b2, eps, clip_gn=0.0, clip=False, max_norm=1.0, grad_scale=1.0):
+    """One plain Adam step in the reference's f32 operation order (optk_adam.cu:38-82, no weight decay):
+    p + ((-lr) * a). Returns (p_new, mu_new, nu_new)."""
+    p, g, mu, nu = (np.asarray(a, dtype=F) for a in (p, g, mu, nu))
+    lr, eps, max_norm, clip_gn, gs = F(lr), F(decimal_of(eps)), F(max_norm), F(clip_gn), F(grad_scale)
+    fb1, fb2, omb1, omb2 = F(b1), F(b2), one_minus(b1), one_minus(b2)
+    bc1, bc2 = bias_correction(b1, t), bias_correction(b2, t)
+    gi = g * gs
+    if clip:
+        gi = (gi / clip_gn) * max_norm
+    mu2 = omb1 * gi + fb1 * mu
+    nu2 = omb2 * (gi * gi) + fb2 * nu
+    with np.errstate(divide="ignore", invalid="ignore"):
+        a = mu2 / (bc1 * (np.sqrt(nu2 / bc2) + eps))
+    return p + (-lr) * a, mu2, nu2
+
+
 def adamh_f64(p, g, mu, nu, t, eta, b1, b2, eps, clip_gn=0.0, clip=False, max_norm=1.0, grad_scale=1.0):
     """The same step in float64 from the same f32 inputs and f32 hyper-parameters."""
     p, g, mu, nu = (np.asarray(a, dtype=np.float64) for a in (p, g, mu, nu))

@@ -207,3 +207,24 @@ def test_full_size_head_keeps_its_norm():
     assert np.array_equal(M[sub].cpu().numpy(), mu_w) and np.array_equal(Vv[sub].cpu().numpy(), nu_w)
     assert torch.equal(W16.view(-1)[sub], P[sub].bfloat16())
     lib().nm_head_adamh_destroy(h)
+
+
+@pytest.mark.parametrize("shape,t,clip", [((1, 2048), 1, False), ((96, 64), 3, True), ((33, 7), 40, True)])
+def test_plain_adam_is_bit_exact_against_the_oracle(shape, t, clip):
+    """nm_adam_update (the rule of the final norm's gain): every operation is elementwise in the reference's order, so
+    p, mu, nu are bit-equal to the oracle (the reference's own test compares bitwise with host f32,
+    tests/s6/test_engine.cpp:756-761)."""
+    A = _A()
+    from gpu_common import lib, nmce
+    p, g, mu, nu = _state(7 * sum(shape) + t, shape)
+    max_norm = 1e-3 if clip else 1e9
+    gn, do_clip = A.clip_state(g, max_norm)
+    P, G, M, V = (torch.from_numpy(a.copy()).cuda() for a in (p, g, mu, nu))
+    P16 = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+    lib().nm_adam_update(nmce.ptr(P), nmce.ptr(P16), nmce.ptr(G), nmce.ptr(M), nmce.ptr(V), shape[0], shape[1], t, 0.008,
+                         0.9, 0.98, 1e-20, float(gn), int(do_clip), max_norm, None, None, None, 0, None)
+    torch.cuda.synchronize()
+    p2, mu2, nu2 = A.adam_f32(p, g, mu, nu, t, 0.008, 0.9, 0.98, 1e-20, clip_gn=gn, clip=do_clip, max_norm=max_norm)
+    assert np.array_equal(M.cpu().numpy(), mu2) and np.array_equal(V.cpu().numpy(), nu2)
+    assert np.array_equal(P.cpu().numpy(), p2)
+    assert torch.equal(P16, P.bfloat16())

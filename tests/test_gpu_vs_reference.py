@@ -155,3 +155,35 @@ def test_adamh_update_against_the_reference_library(shape, t, clip):
     assert r <= 1e-6, f"p rel {r:.3e}"
     assert int((P16 != RP16).sum()) <= 1e-4 * P16.numel()       # an f32 difference of 1 ulp can flip a bf16 tie
     print(f"AdamH {shape} t={t}: p rel vs reference {r:.2e}; host wall of one call {ms:.2f} ms vs reference {rms:.2f} ms")
+
+
+def test_adam_update_against_the_reference_library():
+    """nm_adam_update against the reference's (src/optim/capi_optim.cpp:221-238): bit-equal at t = 1 (bias corrections
+    1 - b exactly); at other t the reference's table uses XLA's f32 pow, this library a correctly rounded one, which may
+    differ by an ulp of b^t: the parameters then agree to 1e-7."""
+    if not os.path.exists(REF_OPT):
+        pytest.skip("oracle/_ref/libref_optim.so was not built (make -C oracle _ref/libref_optim.so)")
+    import ctypes
+    from gpu_common import lib, nmce
+    rdll = ctypes.CDLL(REF_OPT)
+    rdll.nm_adam_update.restype, rdll.nm_adam_update.argtypes = nmce.SIGS["nm_adam_update"]
+    rng = np.random.default_rng(3)
+    shape = (64, 2048)
+    p = (rng.standard_normal(shape) * 0.5 + 1.0).astype(np.float32)
+    g = (rng.standard_normal(shape) * 1e-3).astype(np.float32)
+    mu = (rng.standard_normal(shape) * 1e-3).astype(np.float32)
+    nu = ((rng.standard_normal(shape) * 1e-3) ** 2).astype(np.float32)
+    for t in (1, 25, 1000):
+        out = []
+        for fn in (lib().raw("nm_adam_update"), rdll.nm_adam_update):
+            P, G, M, V = (torch.from_numpy(a.copy()).cuda() for a in (p, g, mu, nu))
+            assert fn(nmce.ptr(P), None, nmce.ptr(G), nmce.ptr(M), nmce.ptr(V), shape[0], shape[1], t, 0.008, 0.9, 0.98,
+                      1e-20, 0.0, 0, 1.0, None, None, None, 0, None) == 0
+            torch.cuda.synchronize()
+            out.append((P, M, V))
+        (P, M, V), (RP, RM, RV) = out
+        assert torch.equal(M, RM) and torch.equal(V, RV)
+        if t == 1:
+            assert torch.equal(P, RP)
+        else:
+            assert float((P.double() - RP.double()).norm() / RP.double().norm()) <= 1e-7
