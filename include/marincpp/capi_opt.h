@@ -50,6 +50,12 @@ int nm_head_adamh_init_master(void* h, const void* w16, float* p_owned, void* st
 int nm_head_adamh_step(void* h, int64_t t, float eta, float b1, float b2, float eps, float max_grad_norm,
                        float grad_scale, const float* grad, float* p_owned, float* mu_owned, float* nu_owned,
                        void* w16, void* stream);
+/* The same update with the all-gather of w16 issued on the reducer's communication stream (it then overlaps whatever
+ * `stream` does next); nm_head_adamh_wait_params makes `stream` wait for it before w16 is read again. */
+int nm_head_adamh_step_async(void* h, int64_t t, float eta, float b1, float b2, float eps, float max_grad_norm,
+                             float grad_scale, const float* grad, float* p_owned, float* mu_owned, float* nu_owned,
+                             void* w16, void* stream);
+int nm_head_adamh_wait_params(void* h, void* stream);
 /* the last step's scalars (4 doubles: sum g^2, sum p^2, sum a^2, sum p a over the whole tensor) copied to the host
  * after the work on `stream` (synchronises that stream) */
 int nm_head_adamh_scalars(void* h, double* out4_host, void* stream);

@@ -30,6 +30,10 @@ struct AdamHStep {
   // docs/spec/optim.md:322-335); 0 = computed here as f32(1 - pow(f32(b), t)) with the power taken in f64, which can
   // differ from that table by one ulp of b^t (AdamH divides the factor out again, plain Adam does not)
   float bc1 = 0.f, bc2 = 0.f;
+  // With a reducer: run the all-gather of the bf16 replica on the reducer's communication stream instead of `st` (the
+  // reference's ParamGather design, include/marincpp/comm.hpp:60-71: the gather of step k travels while the trunk of
+  // step k + 1 runs); whatever reads the replica next must call wait_params first.
+  bool gather_on_comm_stream = false;
 };
 
 class HeadAdamH {
@@ -55,6 +59,9 @@ class HeadAdamH {
   void step(const AdamHStep& s, const float* grad, float* p_owned, float* mu_owned, float* nu_owned, bf16_t* w16,
             cudaStream_t st);
 
+  // `st` waits for the last all-gather issued with gather_on_comm_stream (no-op otherwise)
+  void wait_params(cudaStream_t st);
+
   // the step's scalars on the device (f64: sum g^2, sum p^2, sum a^2, sum p a over the whole tensor), for tests
   const double* scalars() const { return scal_; }
 
@@ -66,6 +73,8 @@ class HeadAdamH {
   int64_t owned_ = 0;
   double* scal_ = nullptr;
   double* partial_ = nullptr;
+  cudaEvent_t applied_ = nullptr, gathered_ = nullptr;
+  bool gather_pending_ = false;
 };
 
 // The reference's one-tensor entry point (include/marincpp/capi.h:107-110, src/optim/capi_optim.cpp:202-219): the

@@ -74,7 +74,11 @@ HeadAdamH::HeadAdamH(int V, int D, GradReducer* reducer) : impl_(new Impl), redu
     NM_CUDA(cudaMalloc(&scal_, opt::kNumScalars * sizeof(double)));
     NM_CUDA(cudaMalloc(&partial_, size_t(opt::kMaxBlocksTotal) * 3 * sizeof(double)));
     NM_CUDA(cudaMemset(scal_, 0, opt::kNumScalars * sizeof(double)));
+    NM_CUDA(cudaEventCreateWithFlags(&applied_, cudaEventDisableTiming));
+    NM_CUDA(cudaEventCreateWithFlags(&gathered_, cudaEventDisableTiming));
   } catch (...) {
+    if (applied_) cudaEventDestroy(applied_);
+    if (gathered_) cudaEventDestroy(gathered_);
     if (scal_) cudaFree(scal_);
     if (partial_) cudaFree(partial_);
     delete impl_;
@@ -83,6 +87,8 @@ HeadAdamH::HeadAdamH(int V, int D, GradReducer* reducer) : impl_(new Impl), redu
 }
 
 HeadAdamH::~HeadAdamH() {
+  if (applied_) cudaEventDestroy(applied_);
+  if (gathered_) cudaEventDestroy(gathered_);
   if (scal_) cudaFree(scal_);
   if (partial_) cudaFree(partial_);
   delete impl_;
@@ -120,14 +126,30 @@ void HeadAdamH::step(const AdamHStep& s, const float* grad, float* p_owned, floa
   opt::launch_apply(r, p_owned, mu_owned, nu_owned, w16, h, scal_, st);
   if (comm && w16) {
     // every bucket of the bf16 replica is completed from its owners' parts
+    cudaStream_t gs = st;
+    if (s.gather_on_comm_stream) {
+      gs = comm->stream();
+      NM_CUDA(cudaEventRecord(applied_, st));
+      NM_CUDA(cudaStreamWaitEvent(gs, applied_, 0));
+    }
     comm->group_start();
     for (int b = 0; b < r.n; ++b) {
       int v0, v1;
       reducer_->range(b, v0, v1);
-      comm->allgather(w16 + int64_t(v0) * D_, r.len[b], DType::bf16, st);
+      comm->allgather(w16 + int64_t(v0) * D_, r.len[b], DType::bf16, gs);
     }
     comm->group_end();
+    if (s.gather_on_comm_stream) {
+      NM_CUDA(cudaEventRecord(gathered_, gs));
+      gather_pending_ = true;
+    }
   }
+}
+
+void HeadAdamH::wait_params(cudaStream_t st) {
+  if (!gather_pending_) return;
+  NM_CUDA(cudaStreamWaitEvent(st, gathered_, 0));
+  gather_pending_ = false;
 }
 
 void adamh_update(float* p, bf16_t* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
@@ -250,6 +272,19 @@ int nm_head_adamh_step(void* h, int64_t t, float eta, float b1, float b2, float 
     s.t = t, s.eta = eta, s.b1 = b1, s.b2 = b2, s.eps = eps, s.max_grad_norm = max_grad_norm, s.grad_scale = grad_scale;
     H(h)->step(s, grad, p_owned, mu_owned, nu_owned, static_cast<nm::bf16_t*>(w16), S(stream));
   });
+}
+int nm_head_adamh_step_async(void* h, int64_t t, float eta, float b1, float b2, float eps, float max_grad_norm,
+                             float grad_scale, const float* grad, float* p_owned, float* mu_owned, float* nu_owned,
+                             void* w16, void* stream) {
+  return nm::capi_call([&] {
+    nm::AdamHStep s;
+    s.t = t, s.eta = eta, s.b1 = b1, s.b2 = b2, s.eps = eps, s.max_grad_norm = max_grad_norm, s.grad_scale = grad_scale;
+    s.gather_on_comm_stream = true;
+    H(h)->step(s, grad, p_owned, mu_owned, nu_owned, static_cast<nm::bf16_t*>(w16), S(stream));
+  });
+}
+int nm_head_adamh_wait_params(void* h, void* stream) {
+  return nm::capi_call([&] { H(h)->wait_params(S(stream)); });
 }
 int nm_head_adamh_scalars(void* h, double* out4_host, void* stream) {
   return nm::capi_call([&] {

@@ -67,6 +67,8 @@ SIGS = {
     "nm_head_adamh_ranges": (I32, [VP, I32, VP, VP, VP, VP]),
     "nm_head_adamh_init_master": (I32, [VP, VP, VP, VP]),
     "nm_head_adamh_step": (I32, [VP, I64, F32, F32, F32, F32, F32, F32, VP, VP, VP, VP, VP, VP]),
+    "nm_head_adamh_step_async": (I32, [VP, I64, F32, F32, F32, F32, F32, F32, VP, VP, VP, VP, VP, VP]),
+    "nm_head_adamh_wait_params": (I32, [VP, VP]),
     "nm_head_adamh_scalars": (I32, [VP, VP, VP]),
 }
 NO_STATUS = {"nm_version", "nm_last_error", "nm_device_arch", "nm_ce_workspace_bytes", "nm_ce_set_backends",

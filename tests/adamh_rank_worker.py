@@ -159,6 +159,19 @@ def main():
     allw = [torch.empty_like(w16) for _ in range(world)]
     dist.all_gather(allw, w16)
     assert all(torch.equal(allw[0], x) for x in allw), "the replicas differ between ranks"
+    # the same step with the all-gather on the communication stream: the replica is complete after wait_params and
+    # bit-equal to the one gathered on the compute stream
+    dw.copy_(torch.from_numpy(grads[rank]).to(dev))
+    w16b = torch.from_numpy(p).to(dev).bfloat16()
+    lib.nm_head_adamh_init_master(opt, nmce.ptr(w16b), nmce.ptr(p_own), None)
+    mu_own.copy_(torch.from_numpy(mu.reshape(-1))[idx].to(dev))
+    nu_own.copy_(torch.from_numpy(nu.reshape(-1))[idx].to(dev))
+    lib.nm_grad_reducer_reduce_all(red, None)
+    lib.nm_head_adamh_step_async(opt, t, HY["eta"], HY["b1"], HY["b2"], HY["eps"], max_norm, 1.0, nmce.ptr(dw),
+                                 nmce.ptr(p_own), nmce.ptr(mu_own), nmce.ptr(nu_own), nmce.ptr(w16b), None)
+    lib.nm_head_adamh_wait_params(opt, None)
+    torch.cuda.synchronize()
+    assert torch.equal(w16b, w16), f"rank {rank}: the replica gathered on the communication stream differs"
     if rank == 0:
         print(f"nccl world {world}: ZeRO-1 AdamH p rel {r:.2e}, {mism} bf16 ties")
     dist.barrier()
