@@ -463,3 +463,23 @@ def test_suggested_chunk_rows():
     assert lib().nm_ce_suggest_chunk_rows(131072) == min(131072, 128 * sms)
     assert lib().nm_ce_suggest_chunk_rows(1000) == 1000
     assert lib().nm_ce_suggest_chunk_rows(0) == 1
+
+
+@pytest.mark.parametrize("T,D,V,chunk", [(3000, 512, 8256, 1024), (2500, 1024, 16400, 2500), (700, 2048, 8256, 512)])
+def test_cta_pairs_give_the_same_bits(T, D, V, chunk):
+    """One CTA per tile and a CTA pair per tile (tcgen05 cta_group::2) add the same products in the same order: every
+    output is bit-identical, for each of the three contractions separately and for all together, on ragged shapes."""
+    from gpu_common import O, grad_scale_dev, lib, run_ce, same_bits, to_dev
+    x, w, y, wt = O.make_inputs(T, D, V, seed=17, ignore_frac=0.05)
+    X, W, Y, WT = to_dev(x, w, y, wt)
+    gs = grad_scale_dev(WT)
+    try:
+        lib().nm_ce_set_cta_pair(0, 0, 0)
+        a = run_ce(X, W, Y, WT, gs, chunk=chunk, z_loss=1e-4)
+        for mode in ((1, 0, 0), (0, 1, 0), (0, 0, 1), (1, 1, 1)):
+            lib().nm_ce_set_cta_pair(*mode)
+            b = run_ce(X, W, Y, WT, gs, chunk=chunk, z_loss=1e-4)
+            for i, n in enumerate(("loss", "lse", "dx", "dw", "loss_partial")):
+                assert same_bits(a[i], b[i]), f"pairs {mode}: {n} differs"
+    finally:
+        lib().nm_ce_set_cta_pair(-1, -1, -1)     # back to the per-launch choice
