@@ -3,6 +3,7 @@
 // reference's src/kernels/cross_entropy/ce_api.cpp: check_shape :52-57, the requirements of run :133-145, the chunk
 // loop :153-239 (dW before dX so dX may overwrite x), readout :243-275.
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <algorithm>
 #include <map>
@@ -146,7 +147,13 @@ void profile_read(double* ms, int* launches) {
   g_prof.used = 0;
 }
 
+// Every launch of the path also sits in an NVTX range named after its kernel class (header-only NVTX 3: a no-op
+// unless a profiler is attached), so that ncu / nsys can select e.g. `--nvtx --nvtx-include "ce.logits/"`.
+static const char* const kProfNames[kProfClasses] = {"ce.logits", "ce.finalize", "ce.dlogits", "ce.dw", "ce.dx",
+                                                     "ce.chunk_loss"};
+
 ProfScope::ProfScope(int cls, cudaStream_t st) : slot_(-1), st_(st) {
+  nvtxRangePushA(kProfNames[cls]);
   if (!g_prof.on) return;
   std::lock_guard<std::mutex> lk(g_prof.mu);
   if (g_prof.used >= int(g_prof.cls.size())) return;
@@ -156,6 +163,7 @@ ProfScope::ProfScope(int cls, cudaStream_t st) : slot_(-1), st_(st) {
 }
 ProfScope::~ProfScope() {
   if (slot_ >= 0) cudaEventRecord(g_prof.ev[2 * slot_ + 1], st_);
+  nvtxRangePop();
 }
 
 // ------------------------------------------------------------------------------------------------ one call

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 #include <nccl.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <cstdlib>
 #include <cstring>
@@ -186,6 +187,8 @@ GradReducer::~GradReducer() {
 void GradReducer::bucket_ready(int b, cudaStream_t compute) {
   NM_REQUIRE(b >= 0 && b < n_buckets(), "grad reducer: bucket index");
   cudaStream_t cs = comm_.stream();
+  nvtxRangePushA(to_owners_ ? "ce.dw_bucket_reduce_scatter" : "ce.dw_bucket_allreduce");
+  struct Pop { ~Pop() { nvtxRangePop(); } } pop;
   NM_CUDA(cudaEventRecord(ready_[b], compute));
   NM_CUDA(cudaStreamWaitEvent(cs, ready_[b], 0));
   float* g = grad_ + int64_t(v0_[b]) * D_;
