@@ -483,3 +483,37 @@ def test_cta_pairs_give_the_same_bits(T, D, V, chunk):
                 assert same_bits(a[i], b[i]), f"pairs {mode}: {n} differs"
     finally:
         lib().nm_ce_set_cta_pair(-1, -1, -1)     # back to the per-launch choice
+
+
+@pytest.mark.parametrize("T,D,V,chunk", [(1000, 264, 1001, 384), (130, 512, 8256, 64), (2049, 1024, 640, 2049)])
+def test_outputs_stay_inside_their_buffers(T, D, V, chunk):
+    """Every output (dx, dw, loss, lse, loss_partial) sits between two guard bands of 0xA5 bytes that must survive the
+    call, on ragged shapes (rows, columns and the vocabulary not multiples of the tile sizes): the TMA stores and
+    reductions clip at the tensor extents, the direct stores are predicated."""
+    from gpu_common import O, grad_scale_dev, lib, nmce, to_dev
+    x, w, y, wt = O.make_inputs(T, D, V, seed=23, ignore_frac=0.05)
+    X, W, Y, WT = to_dev(x, w, y, wt)
+    gs = grad_scale_dev(WT)
+    G = 4096
+    n_chunks = (T + chunk - 1) // chunk
+
+    def guarded(nbytes):
+        buf = torch.full((G + nbytes + G,), 0xA5, dtype=torch.uint8, device="cuda")
+        return buf, buf[G:G + nbytes]
+
+    bufs = {"dx": guarded(T * D * 2), "dw": guarded(V * D * 4), "loss": guarded(T * 4), "lse": guarded(T * 4),
+            "lp": guarded(n_chunks * 4)}
+    bufs["dw"][1].zero_()
+    ws = nmce.Ws.get(lib().nm_ce_workspace_bytes(1, T, D, V, chunk, 1))
+    p = {k: ctypes.c_void_p(v[1].data_ptr()) for k, v in bufs.items()}
+    lib().nm_fused_linear_ce(1, 0, 1, 1, nmce.ptr(X), nmce.ptr(W), nmce.ptr(Y), nmce.ptr(WT), nmce.ptr(gs), None,
+                             p["loss"], p["lse"], p["lp"], p["dx"], 0, p["dw"], None, 0, 0, T, D, V, chunk,
+                             nmce.ptr(ws), None)
+    torch.cuda.synchronize()
+    for name, (buf, view) in bufs.items():
+        n = view.numel()
+        assert bool((buf[:G] == 0xA5).all()) and bool((buf[G + n:] == 0xA5).all()), f"{name}: a guard band was written"
+    dw = bufs["dw"][1].view(torch.float32).view(V, D)
+    dx = bufs["dx"][1].view(torch.bfloat16).view(T, D)
+    assert bool(torch.isfinite(dw).all()) and bool(torch.isfinite(dx.float()).all())
+    assert float(dw.abs().sum()) > 0 and float(dx.float().abs().sum()) > 0
