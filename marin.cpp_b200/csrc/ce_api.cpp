@@ -180,6 +180,9 @@ void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, c
   NM_REQUIRE(!(a.dx && a.dx == a.x && a.accumulate_dx), "fused CE: dx == x cannot accumulate");
   if (impl != CeImpl::A) NM_REQUIRE(!a.logit_bias, "fused CE: logit_bias is implemented only by implementation A");
   NM_REQUIRE(reinterpret_cast<uintptr_t>(ws) % 256 == 0, "fused CE: the workspace must be 256-byte aligned");
+  // x, w and dw are checked where their tensor maps are made; dx is written with 16-byte vector stores
+  NM_REQUIRE(reinterpret_cast<uintptr_t>(a.dx) % 16 == 0, "fused CE: dx must be 16-byte aligned");
+  NM_REQUIRE(reinterpret_cast<uintptr_t>(a.dw_microbatch) % 16 == 0, "fused CE: dw_microbatch must be 16-byte aligned");
   NM_REQUIRE(device_arch() >= 100, "fused CE: this library holds only sm_100a kernels (tcgen05 / TMEM); the current "
                                    "device is sm_" + std::to_string(device_arch()));
 

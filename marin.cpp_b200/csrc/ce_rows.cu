@@ -235,6 +235,9 @@ void launch_chunk_loss(const float* loss_tok, const float* weight, int rows, flo
 
 void launch_dlogits_inplace(const DzArgs& a, cudaStream_t st) {
   if (a.rows <= 0) return;
+  // 16-byte vector accesses on every row of the store
+  NM_REQUIRE(reinterpret_cast<uintptr_t>(a.store) % 16 == 0 && a.ldS % 8 == 0,
+             "dlogits: the store must be 16-byte aligned with a row pitch that is a multiple of 8 elements");
   if (a.store_f32) {
     k_ce_dlogits_f32<<<std::min(a.rows, sm_count() * 8), 256, 0, st>>>(a);
   } else {

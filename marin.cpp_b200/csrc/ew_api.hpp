@@ -14,6 +14,12 @@
 
 namespace nm::ew {
 
+// the row kernels read and write 16-byte pieces: every (non-null) pointer given to them must be 16-byte aligned
+template <class... P>
+inline bool aligned16(P... p) {
+  return ((reinterpret_cast<uintptr_t>(p) % 16 == 0) && ...);
+}
+
 // Number of gain-gradient partial rows the backward writes for T rows on the current device:
 // min(1024, ceil(T / 16), 4 x SMs) parts of consecutive rows (reference ew_api.hpp:18-21).
 int64_t norm_partial_rows(int64_t T);

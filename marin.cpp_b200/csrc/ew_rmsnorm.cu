@@ -141,6 +141,7 @@ int64_t norm_partial_rows(int64_t T) {
 void rmsnorm_fwd(const bf16_t* x, const bf16_t* gain, bf16_t* y, float* rstd, int64_t T, int D, float eps,
                  cudaStream_t st, Rounding r) {
   NM_REQUIRE(x && gain && T >= 0 && D > 0 && D % 8 == 0, "rmsnorm_fwd: x, gain, D % 8 == 0");
+  NM_REQUIRE(aligned16(x, gain, y), "rmsnorm_fwd: x, gain, y must be 16-byte aligned");
   if (T == 0) return;
   const int grid = int(std::min<int64_t>((T + kRowWarps - 1) / kRowWarps, int64_t(ce::sm_count()) * 8));
   auto X = reinterpret_cast<const __nv_bfloat16*>(x);
@@ -154,6 +155,7 @@ void rmsnorm_fwd(const bf16_t* x, const bf16_t* gain, bf16_t* y, float* rstd, in
 void rmsnorm_bwd_add(const bf16_t* dy, const bf16_t* x, const bf16_t* gain, const float* rstd, const bf16_t* dres,
                      bf16_t* dx, float* dgain_partial, int64_t T, int D, float eps, cudaStream_t st, Rounding r) {
   NM_REQUIRE(dy && x && gain && dx && T >= 0 && D > 0 && D % 8 == 0, "rmsnorm_bwd_add: dy, x, gain, dx, D % 8 == 0");
+  NM_REQUIRE(aligned16(dy, x, gain, dres, dx, dgain_partial), "rmsnorm_bwd_add: every pointer must be 16-byte aligned");
   NM_REQUIRE(D <= kMaxPieces * 32 * 8, "rmsnorm_bwd_add: D <= 8192");
   if (T == 0) return;
   const int64_t parts = norm_partial_rows(T);

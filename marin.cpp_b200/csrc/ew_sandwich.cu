@@ -217,6 +217,8 @@ void sandwich_tail_fwd(const bf16_t* branch, const bf16_t* x_in, const bf16_t* g
                        cudaStream_t st, Rounding r) {
   NM_REQUIRE(branch && x_in && g_next && x_out && T >= 0 && D > 0 && D % 8 == 0,
              "sandwich_tail_fwd: branch, x_in, g_next, x_out required; D % 8 == 0");
+  NM_REQUIRE(aligned16(branch, x_in, g_post, g_next, x_out, a_next), "sandwich_tail_fwd: every row pointer must be "
+                                                                     "16-byte aligned");
   if (T == 0) return;
   const int grid = int(std::min<int64_t>((T + kRowWarps - 1) / kRowWarps, int64_t(ce::sm_count()) * 8));
   auto B = [](const bf16_t* p) { return reinterpret_cast<const __nv_bfloat16*>(p); };
@@ -236,6 +238,8 @@ void sandwich_tail_bwd(const bf16_t* dx_out, const bf16_t* da_next, const bf16_t
                        cudaStream_t st, Rounding r) {
   NM_REQUIRE(dx_out && da_next && x_out && g_next && dx_in && dbranch && T >= 0 && D > 0 && D % 8 == 0,
              "sandwich_tail_bwd: dx_out, da_next, x_out, g_next, dx_in, dbranch required; D % 8 == 0");
+  NM_REQUIRE(aligned16(dx_out, da_next, x_out, g_next, branch, g_post, dx_in, dbranch, pg_next, pg_post),
+             "sandwich_tail_bwd: every row pointer must be 16-byte aligned");
   NM_REQUIRE(!g_post || branch, "sandwich_tail_bwd: a post-norm needs the branch output");
   NM_REQUIRE(D <= kMaxPieces * 32 * 8, "sandwich_tail_bwd: D <= 8192");
   if (T == 0) return;

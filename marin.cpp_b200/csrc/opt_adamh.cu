@@ -60,23 +60,23 @@ __device__ __forceinline__ float adam_dir(float mu, float nu, const Hyper& h) {
   return dvd(mu, mul(h.bc1, add(__fsqrt_rn(dvd(nu, h.bc2)), h.eps)));
 }
 
-// A range is walked in float4 units when its global and compact offsets are multiples of 4 (then every pointer is
-// 16-byte aligned, the bf16 copy 8-byte); the last len % 4 elements, or the whole range otherwise, go one by one.
+// A range is walked in float4 units when every pointer it touches (already offset to the range) is 16-byte aligned
+// (the bf16 copy 8-byte); the last len % 4 elements, or the whole range otherwise, go one by one.
 struct Walk {
   int64_t quads, len;
-  bool vec;
 };
-__device__ __forceinline__ Walk walk_of(const Ranges& r, int y) {
-  const bool vec = ((r.goff[y] | r.coff[y]) & 3) == 0;
-  return Walk{vec ? r.len[y] >> 2 : 0, r.len[y], vec};
+__device__ __forceinline__ bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+__device__ __forceinline__ bool al8(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7) == 0; }
+__device__ __forceinline__ Walk walk_of(const Ranges& r, int y, bool aligned) {
+  return Walk{aligned ? r.len[y] >> 2 : 0, r.len[y]};
 }
 
 // ------------------------------------------------------------------------------------------------ sum of g^2
 __global__ void __launch_bounds__(kThreads) k_sumsq(const float* __restrict__ g, Ranges r, float grad_scale,
                                                     double* __restrict__ partial) {
   const int y = blockIdx.y;
-  const Walk wk = walk_of(r, y);
   const float* gp = g + r.goff[y];
+  const Walk wk = walk_of(r, y, al16(gp));
   double s = 0.0;
   const int64_t stride = int64_t(gridDim.x) * kThreads, i0 = int64_t(blockIdx.x) * kThreads + threadIdx.x;
   for (int64_t q = i0; q < wk.quads; q += stride) {
@@ -106,12 +106,12 @@ __global__ void __launch_bounds__(kThreads) k_adamh_moments(Ranges r, const floa
                                                             const double* __restrict__ scal,
                                                             double* __restrict__ partial) {
   const int y = blockIdx.y;
-  const Walk wk = walk_of(r, y);
   const Clip cl = clip_of(h, scal);
   const float* gp = g + r.goff[y];
   const float* pp = p + r.coff[y];
   float* mp = mu + r.coff[y];
   float* vp = nu + r.coff[y];
+  const Walk wk = walk_of(r, y, al16(gp) && al16(pp) && al16(mp) && al16(vp));
   double spp = 0.0, saa = 0.0, spa = 0.0;
   auto elem = [&](float gv, float pv, float& m, float& v) {
     const float gi = clipped(gv, h, cl);
@@ -154,7 +154,6 @@ __global__ void __launch_bounds__(kThreads) k_adamh_apply(Ranges r, float* __res
                                                           __nv_bfloat16* __restrict__ w16, Hyper h,
                                                           const double* __restrict__ scal) {
   const int y = blockIdx.y;
-  const Walk wk = walk_of(r, y);
   // the tensor's norms, from the sums over every rank's ranges
   const float n = norm_of(scal[kSumPP]);
   const float m_floor = fmax_nan(norm_of(scal[kSumAA]), 1e-10f);
@@ -165,6 +164,7 @@ __global__ void __launch_bounds__(kThreads) k_adamh_apply(Ranges r, float* __res
   const float* mp = mu + r.coff[y];
   const float* vp = nu + r.coff[y];
   __nv_bfloat16* wp = w16 ? w16 + r.goff[y] : nullptr;
+  const Walk wk = walk_of(r, y, al16(pp) && al16(mp) && al16(vp) && (!wp || al8(wp)));
   auto elem = [&](float pv, float m, float v) {
     const float a = adam_dir(m, v, h);
     const float w = sub(pv, dvd(mul(mul(h.eta, a), n), m_floor));
@@ -203,7 +203,6 @@ __global__ void __launch_bounds__(kThreads) k_adam(Ranges r, const float* __rest
                                                    __nv_bfloat16* __restrict__ w16, Hyper h,
                                                    const double* __restrict__ scal) {
   const int y = blockIdx.y;
-  const Walk wk = walk_of(r, y);
   const Clip cl = clip_of(h, scal);
   const float neg_lr = -h.eta;
   const float* gp = g + r.goff[y];
@@ -211,6 +210,7 @@ __global__ void __launch_bounds__(kThreads) k_adam(Ranges r, const float* __rest
   float* mp = mu + r.coff[y];
   float* vp = nu + r.coff[y];
   __nv_bfloat16* wp = w16 ? w16 + r.goff[y] : nullptr;
+  const Walk wk = walk_of(r, y, al16(gp) && al16(pp) && al16(mp) && al16(vp) && (!wp || al8(wp)));
   auto elem = [&](float gv, float& pv, float& m, float& v) {
     const float gi = clipped(gv, h, cl);
     m = add(mul(h.one_minus_b1, gi), mul(h.b1, m));

@@ -228,3 +228,33 @@ def test_plain_adam_is_bit_exact_against_the_oracle(shape, t, clip):
     assert np.array_equal(M.cpu().numpy(), mu2) and np.array_equal(V.cpu().numpy(), nu2)
     assert np.array_equal(P.cpu().numpy(), p2)
     assert torch.equal(P16, P.bfloat16())
+
+
+def test_update_stays_inside_its_buffers():
+    """p, mu, nu and the bf16 copy between guard bands, with an element count that is not a multiple of 4 and buffers
+    that are not 16-byte aligned (the scalar walk): nothing outside the tensor is written."""
+    from gpu_common import lib, nmce
+    R, C = 37, 11
+    n = R * C
+    p, g, mu, nu = _state(55, (R, C))
+    G = 1024
+
+    def guarded(arr, dtype, esz):
+        buf = torch.full((G + 4 + n * esz + G,), 0xA5, dtype=torch.uint8, device="cuda")
+        view = buf[G + 4:G + 4 + n * esz].view(dtype)          # 4 bytes past a 16-byte boundary
+        if arr is not None:
+            view.copy_(torch.from_numpy(arr.reshape(-1)).cuda())
+        return buf, view
+
+    bp, vp = guarded(p, torch.float32, 4)
+    bm, vm = guarded(mu, torch.float32, 4)
+    bv, vv = guarded(nu, torch.float32, 4)
+    b16, v16 = guarded(None, torch.bfloat16, 2)
+    G_ = torch.from_numpy(g.copy()).cuda()
+    lib().nm_adamh_update(nmce.ptr(vp), nmce.ptr(v16), nmce.ptr(G_), nmce.ptr(vm), nmce.ptr(vv), R, C, 2, 0.02, 0.9, 0.98,
+                          1e-20, 0.0, 0, 1.0, None, None, None, 0, None)
+    torch.cuda.synchronize()
+    for name, buf, esz in (("p", bp, 4), ("mu", bm, 4), ("nu", bv, 4), ("p16", b16, 2)):
+        assert bool((buf[:G + 4] == 0xA5).all()) and bool((buf[G + 4 + n * esz:] == 0xA5).all()), f"{name}: guard written"
+    assert torch.equal(v16, vp.bfloat16())
+    assert abs(float(vp.double().norm()) - float(np.linalg.norm(p.astype(np.float64)))) <= 1e-6 * float(np.linalg.norm(p))

@@ -303,6 +303,21 @@ def test_argument_errors_on_device():
         run_ce(X, W, Y, WT, gs, dw_round=1)
     assert e.value.status == 1
     assert lib().nm_ce_device_arch() == 100 and lib().nm_device_arch() == 100
+    # pointers the kernels access with 16-byte vectors or TMA must be 16-byte aligned: refused on the host, no launch
+    big = torch.zeros(64 * 64 + 8, dtype=torch.bfloat16, device="cuda")
+    odd_dx = big[4:4 + 64 * 64].view(64, 64)               # 8 bytes past a 16-byte boundary
+    with pytest.raises(nmce.NmError) as e:
+        run_ce(X, W, Y, WT, gs, dx=odd_dx)
+    assert e.value.status == 1 and "16-byte aligned" in str(e.value)
+    odd_x = big[4:4 + 64 * 64].view(64, 64)
+    with pytest.raises(nmce.NmError) as e:
+        run_ce(odd_x, W, Y, WT, gs)
+    assert e.value.status == 1 and "16-byte aligned" in str(e.value)
+    from gpu_common import lib as _lib
+    with pytest.raises(nmce.NmError) as e:                  # the RMSNorm entry point checks its row pointers too
+        _lib().nm_rmsnorm_fwd(1, 0, nmce.ptr(odd_x), nmce.ptr(big), nmce.ptr(big), nmce.ptr(torch.zeros(64, device="cuda")),
+                              64, 64, 1e-5, None)
+    assert e.value.status == 1 and "16-byte aligned" in str(e.value)
 
 
 def test_bounded_wait_times_out_and_reports():
