@@ -433,11 +433,17 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     comm_events = [] if reducer else None
     e0.record(stream)
+    step_marks = []
     for _ in range(args.steps):
         step()
+        m = torch.cuda.Event(enable_timing=True)
+        m.record(stream)
+        step_marks.append(m)
     e1.record(stream)
     barrier()
     clocks = sampler.stop()
+    # per-step durations on this rank (the headline stays the total over the K steps, max over ranks)
+    per_step = [a.elapsed_time(b) for a, b in zip([e0] + step_marks[:-1], step_marks)]
     exposed_comm_ms = None
     if comm_events:
         exposed_comm_ms = sum(comm_events[i].elapsed_time(comm_events[i + 1])
@@ -557,6 +563,7 @@ def main():
     out = {
         "metric": "fused_ce_fwd_bwd_tokens_per_s", "value": tokens / (ms_total * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "ms_per_step_median_rank0": sorted(per_step)[len(per_step) // 2], "ms_per_step_min_rank0": min(per_step),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD[args.config] + (f" [tokens overridden to {T}]" if args.tokens > 0 else ""),
                    "tokens_per_gpu": R * T, "hidden": D, "vocab": V,
