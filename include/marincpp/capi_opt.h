@@ -12,9 +12,11 @@ extern "C" {
 /* reference include/marincpp/capi.h:107-110 (src/optim/capi_optim.cpp:202-219): one AdamH update of one 2-D tensor
  * p[rows, cols] f32 (p16: optional bf16 copy of the new p) from gradient g and moments mu, nu, at update count t >= 1
  * with learning rate eta; when `clip` is non-zero the gradient is first scaled as (g / clip_gn) * max_norm.
- * block_of_row / block_lr_mult / block_frozen (row blocks with their own learning rates and norms) are not
- * supported here: pass NULL, NULL, NULL, 0 (anything else returns NM_ERR_INVALID). Unlike the reference's, this call
- * does not synchronise the stream. */
+ * Row blocks (optional; NULL, NULL, NULL, 0 = none; device arrays): block_of_row[rows] in [0, n_blocks),
+ * block_lr_mult[n_blocks] (NULL: 1), block_frozen[n_blocks] (NULL: none). A block uses eta * its multiplier and takes
+ * its AdamH norms over its own rows; the rows of a frozen block keep p, mu, nu and p16. With row blocks the call copies
+ * block_of_row to the host to validate it and synchronises the stream (as the reference's does); without, it does not
+ * synchronise. */
 int nm_adamh_update(float* p, void* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
                     float eta, float b1, float b2, float eps, float clip_gn, int clip, float max_norm,
                     const int32_t* block_of_row, const float* block_lr_mult, const uint8_t* block_frozen,
@@ -22,7 +24,7 @@ int nm_adamh_update(float* p, void* p16, const float* g, float* mu, float* nu, i
 
 /* reference include/marincpp/capi.h:111-114: one plain Adam update of one tensor, p += (-adam_lr) a with the same
  * moments, bias corrections and clip as above and no projection (the rule of the final norm's gain, whose gradient the
- * readout entry point produces). Row blocks: as above, not supported. */
+ * readout entry point produces). Row blocks as above (multiplier on adam_lr, frozen blocks). */
 int nm_adam_update(float* p, void* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
                    float adam_lr, float b1, float b2, float eps, float clip_gn, int clip, float max_norm,
                    const int32_t* block_of_row, const float* block_lr_mult, const uint8_t* block_frozen,

@@ -78,13 +78,25 @@ class HeadAdamH {
 };
 
 // The reference's one-tensor entry point (include/marincpp/capi.h:107-110, src/optim/capi_optim.cpp:202-219): the
-// whole [rows, cols] tensor on one GPU, clip state given by the caller. Row blocks (block_of_row) are not supported.
+// whole [rows, cols] tensor on one GPU, clip state given by the caller. Optional row blocks (device arrays; nullptr /
+// 0 = none): block_of_row[rows] in [0, n_blocks), block_lr_mult[n_blocks] (nullable: 1), block_frozen[n_blocks]
+// (nullable: none); a block has its own learning-rate multiplier and its own AdamH norms, a frozen block's rows keep
+// p, mu, nu and enter no norm (reference src/optim/capi_optim.cpp:103-128). With row blocks the call copies
+// block_of_row to the host to validate it and synchronises the stream, as the reference's does.
+struct RowBlocks {
+  const int32_t* block_of_row = nullptr;
+  const float* block_lr_mult = nullptr;
+  const uint8_t* block_frozen = nullptr;
+  int n_blocks = 0;
+};
 void adamh_update(float* p, bf16_t* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
-                  float eta, float b1, float b2, float eps, float clip_gn, bool clip, float max_norm, cudaStream_t st);
+                  float eta, float b1, float b2, float eps, float clip_gn, bool clip, float max_norm, cudaStream_t st,
+                  const RowBlocks& blocks = RowBlocks{});
 
 // The reference's one-tensor Adam entry point (include/marincpp/capi.h:111-114): p += (-adam_lr) a, no projection; for
-// the tensors beside the head on this path (the final norm's gain). Row blocks are not supported.
+// the tensors beside the head on this path (the final norm's gain). Row blocks as above.
 void adam_update(float* p, bf16_t* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
-                 float adam_lr, float b1, float b2, float eps, float clip_gn, bool clip, float max_norm, cudaStream_t st);
+                 float adam_lr, float b1, float b2, float eps, float clip_gn, bool clip, float max_norm, cudaStream_t st,
+                 const RowBlocks& blocks = RowBlocks{});
 
 }  // namespace nm

@@ -245,6 +245,111 @@ __global__ void __launch_bounds__(kThreads) k_adam(Ranges r, const float* __rest
   }
 }
 
+// ------------------------------------------------------------------------------------------------ row blocks
+// The one-tensor entry points with a row partition (reference src/optim/capi_optim.cpp:103-128, optk_adam.cu:28-31,
+// 84-221 with sl.block >= 0): every row belongs to a block; a block has its own learning-rate multiplier, may be
+// frozen (its rows keep p, mu, nu and enter no norm), and AdamH takes its norms over the block's rows instead of the
+// whole tensor. One CUDA block walks whole rows (a row's block id is uniform), writes the row's f64 sums, and a second
+// kernel adds the rows of each block in ascending row order per thread, then by the fixed tree: deterministic.
+__device__ __forceinline__ bool blk_frozen(const BlockTab& bt, int b) { return bt.frozen && bt.frozen[b] != 0; }
+__device__ __forceinline__ float blk_lr(const BlockTab& bt, int b, float lr) {
+  return mul(mul(lr, 1.0f), bt.lr_mult ? bt.lr_mult[b] : 1.0f);   // lr * lr_scale * block multiplier
+}
+
+__global__ void __launch_bounds__(kThreads) k_blk_adamh_moments(const float* __restrict__ g, const float* __restrict__ p,
+                                                                float* __restrict__ mu, float* __restrict__ nu,
+                                                                int64_t rows, int64_t cols, Hyper h, BlockTab bt,
+                                                                double* __restrict__ row_partial) {
+  const Clip cl = clip_of(h, nullptr);
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int b = bt.block_of_row[row];
+    double spp = 0.0, saa = 0.0, spa = 0.0;
+    if (!blk_frozen(bt, b)) {
+      const int64_t o = row * cols;
+      for (int64_t c = threadIdx.x; c < cols; c += kThreads) {
+        const float gi = clipped(g[o + c], h, cl);
+        const float m = add(mul(h.one_minus_b1, gi), mul(h.b1, mu[o + c]));
+        const float v = add(mul(h.one_minus_b2, mul(gi, gi)), mul(h.b2, nu[o + c]));
+        mu[o + c] = m;
+        nu[o + c] = v;
+        const float a = adam_dir(m, v, h), pv = p[o + c];
+        spp += sq(pv);
+        saa += sq(a);
+        spa = fma(static_cast<double>(pv), static_cast<double>(a), spa);
+      }
+    }
+    spp = block_sum(spp);
+    saa = block_sum(saa);
+    spa = block_sum(spa);
+    if (threadIdx.x == 0) {
+      row_partial[row * 3] = spp, row_partial[row * 3 + 1] = saa, row_partial[row * 3 + 2] = spa;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) k_blk_reduce(const double* __restrict__ row_partial,
+                                                         const int32_t* __restrict__ block_of_row, int64_t rows,
+                                                         double* __restrict__ blk_scal) {
+  const int b = blockIdx.x;
+  double s[3] = {0.0, 0.0, 0.0};
+  for (int64_t row = threadIdx.x; row < rows; row += kThreads)
+    if (block_of_row[row] == b) {
+      s[0] += row_partial[row * 3], s[1] += row_partial[row * 3 + 1], s[2] += row_partial[row * 3 + 2];
+    }
+  for (int j = 0; j < 3; ++j) {
+    const double t = block_sum(s[j]);
+    if (threadIdx.x == 0) blk_scal[b * 3 + j] = t;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) k_blk_adamh_apply(float* __restrict__ p, const float* __restrict__ mu,
+                                                              const float* __restrict__ nu,
+                                                              __nv_bfloat16* __restrict__ w16, int64_t rows, int64_t cols,
+                                                              Hyper h, BlockTab bt, const double* __restrict__ blk_scal) {
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int b = bt.block_of_row[row];
+    const int64_t o = row * cols;
+    if (blk_frozen(bt, b)) continue;          // p, mu, nu and the bf16 copy keep their values
+    const double pp = blk_scal[b * 3], aa = blk_scal[b * 3 + 1], pa = blk_scal[b * 3 + 2];
+    const float eta = blk_lr(bt, b, h.eta);
+    const float n = norm_of(pp);
+    const float m_floor = fmax_nan(norm_of(aa), 1e-10f);
+    const double c_ = static_cast<double>(eta) * static_cast<double>(n) / static_cast<double>(m_floor);
+    const float nw = norm_of(pp - 2.0 * c_ * pa + c_ * c_ * aa);
+    for (int64_t c = threadIdx.x; c < cols; c += kThreads) {
+      const float pv = p[o + c];
+      const float a = adam_dir(mu[o + c], nu[o + c], h);
+      const float w = sub(pv, dvd(mul(mul(eta, a), n), m_floor));
+      const float pn = add(pv, sub(mul(dvd(w, nw), n), pv));
+      p[o + c] = pn;
+      if (w16) w16[o + c] = __float2bfloat16_rn(pn);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) k_blk_adam(const float* __restrict__ g, float* __restrict__ p,
+                                                       float* __restrict__ mu, float* __restrict__ nu,
+                                                       __nv_bfloat16* __restrict__ w16, int64_t rows, int64_t cols,
+                                                       Hyper h, BlockTab bt) {
+  const Clip cl = clip_of(h, nullptr);
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int b = bt.block_of_row[row];
+    const int64_t o = row * cols;
+    if (blk_frozen(bt, b)) continue;          // p, mu, nu and the bf16 copy keep their values
+    const float neg_lr = -blk_lr(bt, b, h.eta);
+    for (int64_t c = threadIdx.x; c < cols; c += kThreads) {
+      const float gi = clipped(g[o + c], h, cl);
+      const float m = add(mul(h.one_minus_b1, gi), mul(h.b1, mu[o + c]));
+      const float v = add(mul(h.one_minus_b2, mul(gi, gi)), mul(h.b2, nu[o + c]));
+      mu[o + c] = m;
+      nu[o + c] = v;
+      const float pv = add(p[o + c], mul(neg_lr, adam_dir(m, v, h)));
+      p[o + c] = pv;
+      if (w16) w16[o + c] = __float2bfloat16_rn(pv);
+    }
+  }
+}
+
 // master copy from the bf16 replica: p[compact] = f32(w16[global]) over the owned ranges
 __global__ void __launch_bounds__(kThreads) k_master_from_bf16(Ranges r, const __nv_bfloat16* __restrict__ w16,
                                                                float* __restrict__ p) {
@@ -296,6 +401,27 @@ void launch_adam(const Ranges& r, const float* g, float* p, float* mu, float* nu
                  const double* scal, cudaStream_t st) {
   if (r.n <= 0) return;
   k_adam<<<dim3(blocks_for(r), r.n), kThreads, 0, st>>>(r, g, p, mu, nu, static_cast<__nv_bfloat16*>(w16), h, scal);
+  NM_CUDA(cudaGetLastError());
+}
+
+namespace {
+int row_grid(int64_t rows) { return int(std::min<int64_t>(rows, int64_t(kMaxBlocksTotal))); }
+}  // namespace
+
+void launch_blk_adamh(const float* g, float* p, float* mu, float* nu, void* w16, int64_t rows, int64_t cols,
+                      const Hyper& h, const BlockTab& bt, double* row_partial, double* blk_scal, cudaStream_t st) {
+  k_blk_adamh_moments<<<row_grid(rows), kThreads, 0, st>>>(g, p, mu, nu, rows, cols, h, bt, row_partial);
+  NM_CUDA(cudaGetLastError());
+  k_blk_reduce<<<bt.n_blocks, kThreads, 0, st>>>(row_partial, bt.block_of_row, rows, blk_scal);
+  NM_CUDA(cudaGetLastError());
+  k_blk_adamh_apply<<<row_grid(rows), kThreads, 0, st>>>(p, mu, nu, static_cast<__nv_bfloat16*>(w16), rows, cols, h, bt,
+                                                         blk_scal);
+  NM_CUDA(cudaGetLastError());
+}
+
+void launch_blk_adam(const float* g, float* p, float* mu, float* nu, void* w16, int64_t rows, int64_t cols,
+                     const Hyper& h, const BlockTab& bt, cudaStream_t st) {
+  k_blk_adam<<<row_grid(rows), kThreads, 0, st>>>(g, p, mu, nu, static_cast<__nv_bfloat16*>(w16), rows, cols, h, bt);
   NM_CUDA(cudaGetLastError());
 }
 

@@ -5,6 +5,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <string>
+#include <vector>
 
 #include "capi_util.hpp"
 #include "marincpp/capi_opt.h"
@@ -42,6 +43,22 @@ opt::Hyper make_hyper(int64_t t, float eta, float b1, float b2, float eps, float
   h.max_norm = 1.f;
   h.clip_gn = 1.f;
   return h;
+}
+
+// Row blocks of a one-tensor call: validated on the host (block ids in range), as the reference does.
+bool make_block_tab(const RowBlocks& rb, int64_t rows, cudaStream_t st, opt::BlockTab& bt) {
+  if (!rb.block_of_row) {
+    NM_REQUIRE(!rb.block_lr_mult && !rb.block_frozen && rb.n_blocks == 0,
+               "optimizer update: block_lr_mult / block_frozen / n_blocks need block_of_row");
+    return false;
+  }
+  NM_REQUIRE(rb.n_blocks > 0 && rb.n_blocks <= 65535, "optimizer update: n_blocks must be in [1, 65535] with block_of_row");
+  std::vector<int32_t> host(static_cast<size_t>(rows));
+  NM_CUDA(cudaMemcpyAsync(host.data(), rb.block_of_row, size_t(rows) * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  NM_CUDA(cudaStreamSynchronize(st));
+  for (int32_t b : host) NM_REQUIRE(b >= 0 && b < rb.n_blocks, "optimizer update: block_of_row out of range");
+  bt = opt::BlockTab{rb.block_of_row, rb.block_lr_mult, rb.block_frozen, rb.n_blocks};
+  return true;
 }
 
 }  // namespace
@@ -153,7 +170,8 @@ void HeadAdamH::wait_params(cudaStream_t st) {
 }
 
 void adamh_update(float* p, bf16_t* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
-                  float eta, float b1, float b2, float eps, float clip_gn, bool clip, float max_norm, cudaStream_t st) {
+                  float eta, float b1, float b2, float eps, float clip_gn, bool clip, float max_norm, cudaStream_t st,
+                  const RowBlocks& blocks) {
   NM_REQUIRE(p && g && mu && nu, "adamh_update: p, g, mu, nu required");
   NM_REQUIRE(rows > 0 && cols > 0, "adamh_update: rows, cols > 0");
   opt::Hyper h = make_hyper(t, eta, b1, b2, eps, 1.0f);
@@ -161,6 +179,20 @@ void adamh_update(float* p, bf16_t* p16, const float* g, float* mu, float* nu, i
   h.clip = clip ? 1 : 0;
   h.clip_gn = clip_gn;
   h.max_norm = max_norm;
+  opt::BlockTab bt{};
+  if (make_block_tab(blocks, rows, st, bt)) {
+    double* scratch = nullptr;
+    const size_t n_doubles = size_t(rows) * 3 + size_t(bt.n_blocks) * 3;
+    NM_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&scratch), n_doubles * sizeof(double), st));
+    try {
+      opt::launch_blk_adamh(g, p, mu, nu, p16, rows, cols, h, bt, scratch, scratch + size_t(rows) * 3, st);
+    } catch (...) {
+      cudaFreeAsync(scratch, st);
+      throw;
+    }
+    NM_CUDA(cudaFreeAsync(scratch, st));
+    return;
+  }
   opt::Ranges r;
   r.n = 1;
   r.goff[0] = 0, r.coff[0] = 0, r.len[0] = rows * cols;
@@ -180,7 +212,8 @@ void adamh_update(float* p, bf16_t* p16, const float* g, float* mu, float* nu, i
 }
 
 void adam_update(float* p, bf16_t* p16, const float* g, float* mu, float* nu, int64_t rows, int64_t cols, int64_t t,
-                 float adam_lr, float b1, float b2, float eps, float clip_gn, bool clip, float max_norm, cudaStream_t st) {
+                 float adam_lr, float b1, float b2, float eps, float clip_gn, bool clip, float max_norm, cudaStream_t st,
+                 const RowBlocks& blocks) {
   NM_REQUIRE(p && g && mu && nu, "adam_update: p, g, mu, nu required");
   NM_REQUIRE(rows > 0 && cols > 0, "adam_update: rows, cols > 0");
   opt::Hyper h = make_hyper(t, adam_lr, b1, b2, eps, 1.0f);
@@ -188,6 +221,11 @@ void adam_update(float* p, bf16_t* p16, const float* g, float* mu, float* nu, in
   h.clip = clip ? 1 : 0;
   h.clip_gn = clip_gn;
   h.max_norm = max_norm;
+  opt::BlockTab bt{};
+  if (make_block_tab(blocks, rows, st, bt)) {
+    opt::launch_blk_adam(g, p, mu, nu, p16, rows, cols, h, bt, st);
+    return;
+  }
   opt::Ranges r;
   r.n = 1;
   r.goff[0] = 0, r.coff[0] = 0, r.len[0] = rows * cols;
@@ -212,10 +250,8 @@ int nm_adamh_update(float* p, void* p16, const float* g, float* mu, float* nu, i
                     const int32_t* block_of_row, const float* block_lr_mult, const uint8_t* block_frozen, int n_blocks,
                     void* stream) {
   return nm::capi_call([&] {
-    NM_REQUIRE(!block_of_row && !block_lr_mult && !block_frozen && n_blocks == 0,
-               "nm_adamh_update: row blocks are not supported by this library (pass NULL, NULL, NULL, 0)");
     nm::adamh_update(p, static_cast<nm::bf16_t*>(p16), g, mu, nu, rows, cols, t, eta, b1, b2, eps, clip_gn, clip != 0,
-                     max_norm, S(stream));
+                     max_norm, S(stream), nm::RowBlocks{block_of_row, block_lr_mult, block_frozen, n_blocks});
   });
 }
 
@@ -224,10 +260,8 @@ int nm_adam_update(float* p, void* p16, const float* g, float* mu, float* nu, in
                    const int32_t* block_of_row, const float* block_lr_mult, const uint8_t* block_frozen, int n_blocks,
                    void* stream) {
   return nm::capi_call([&] {
-    NM_REQUIRE(!block_of_row && !block_lr_mult && !block_frozen && n_blocks == 0,
-               "nm_adam_update: row blocks are not supported by this library (pass NULL, NULL, NULL, 0)");
     nm::adam_update(p, static_cast<nm::bf16_t*>(p16), g, mu, nu, rows, cols, t, adam_lr, b1, b2, eps, clip_gn,
-                    clip != 0, max_norm, S(stream));
+                    clip != 0, max_norm, S(stream), nm::RowBlocks{block_of_row, block_lr_mult, block_frozen, n_blocks});
   });
 }
 

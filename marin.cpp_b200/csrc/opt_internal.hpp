@@ -29,6 +29,15 @@ struct Hyper {
   int clip;
 };
 
+// Row blocks of the one-tensor entry points (device arrays): block id per row, per-block learning-rate multiplier
+// (nullable: 1), per-block frozen flag (nullable: none).
+struct BlockTab {
+  const int32_t* block_of_row;
+  const float* lr_mult;
+  const uint8_t* frozen;
+  int n_blocks;
+};
+
 constexpr int kMaxBlocksTotal = 148 * 8;
 int partial_blocks(const Ranges& r);   // partial slots (of 1 or 3 doubles) a launch over r writes
 
@@ -44,6 +53,11 @@ void launch_apply(const Ranges& r, float* p, const float* mu, const float* nu, v
 // plain Adam in one pass: p += (-eta) a (h.eta is the Adam learning rate); scal is read only with clip_mode 2
 void launch_adam(const Ranges& r, const float* g, float* p, float* mu, float* nu, void* w16, const Hyper& h,
                  const double* scal, cudaStream_t st);
+// the same updates with a row partition; row_partial: rows * 3 doubles, blk_scal: n_blocks * 3 doubles (scratch)
+void launch_blk_adamh(const float* g, float* p, float* mu, float* nu, void* w16, int64_t rows, int64_t cols,
+                      const Hyper& h, const BlockTab& bt, double* row_partial, double* blk_scal, cudaStream_t st);
+void launch_blk_adam(const float* g, float* p, float* mu, float* nu, void* w16, int64_t rows, int64_t cols,
+                     const Hyper& h, const BlockTab& bt, cudaStream_t st);
 void launch_master_from_bf16(const Ranges& r, const void* w16, float* p, cudaStream_t st);
 
 }  // namespace nm::opt

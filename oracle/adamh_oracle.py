@@ -123,3 +123,19 @@ def owned_ranges(V, D, v0, v1, nranks, rank):
         assert n % nranks == 0
         out.append((a * D + rank * (n // nranks), n // nranks))
     return out
+
+
+def with_row_blocks(fn, p, g, mu, nu, t, lr, b1, b2, eps, block_of_row, lr_mult=None, frozen=None, **kw):
+    """A one-tensor update with a row partition (reference src/optim/capi_optim.cpp:103-128): rows of block b use the
+    learning rate f32(lr * mult[b]); AdamH takes its norms over the block's rows; the rows of a frozen block keep p, mu,
+    nu. fn is adamh_f32 or adam_f32 (each block is one independent call of it). Returns (p, mu, nu)."""
+    p, g, mu, nu = (np.array(a, dtype=F, copy=True) for a in (p, g, mu, nu))
+    block_of_row = np.asarray(block_of_row)
+    for b in np.unique(block_of_row):
+        if frozen is not None and frozen[b]:
+            continue
+        rows = block_of_row == b
+        lr_b = F(F(lr) * F(1.0)) * (F(lr_mult[b]) if lr_mult is not None else F(1.0))
+        out = fn(p[rows], g[rows], mu[rows], nu[rows], t, lr_b, b1, b2, eps, **kw)
+        p[rows], mu[rows], nu[rows] = out[0], out[1], out[2]
+    return p, mu, nu

@@ -89,14 +89,18 @@ def test_zero_learning_rate_and_repeat():
     assert all(torch.equal(x, y) for x, y in zip(a, b))
 
 
-def test_rejects_row_blocks_and_bad_arguments():
+def test_bad_arguments():
     from gpu_common import lib, nmce
     x = torch.zeros(8, 8, device="cuda")
-    blk = torch.zeros(8, dtype=torch.int32, device="cuda")
-    with pytest.raises(nmce.NmError) as e:
+    blk = torch.full((8,), 3, dtype=torch.int32, device="cuda")
+    with pytest.raises(nmce.NmError) as e:      # a block id outside [0, n_blocks)
         lib().nm_adamh_update(nmce.ptr(x), None, nmce.ptr(x), nmce.ptr(x), nmce.ptr(x), 8, 8, 1, 0.02, 0.9, 0.98, 1e-20,
-                              0.0, 0, 1.0, nmce.ptr(blk), None, None, 1, None)
-    assert e.value.status == 1 and "row blocks" in str(e.value)
+                              0.0, 0, 1.0, nmce.ptr(blk), None, None, 2, None)
+    assert e.value.status == 1 and "out of range" in str(e.value)
+    with pytest.raises(nmce.NmError) as e:      # multipliers without a partition
+        lib().nm_adamh_update(nmce.ptr(x), None, nmce.ptr(x), nmce.ptr(x), nmce.ptr(x), 8, 8, 1, 0.02, 0.9, 0.98, 1e-20,
+                              0.0, 0, 1.0, None, nmce.ptr(x), None, 2, None)
+    assert e.value.status == 1
     with pytest.raises(nmce.NmError) as e:
         lib().nm_adamh_update(nmce.ptr(x), None, nmce.ptr(x), nmce.ptr(x), nmce.ptr(x), 8, 8, 0, 0.02, 0.9, 0.98, 1e-20,
                               0.0, 0, 1.0, None, None, None, 0, None)
@@ -258,3 +262,44 @@ def test_update_stays_inside_its_buffers():
         assert bool((buf[:G + 4] == 0xA5).all()) and bool((buf[G + 4 + n * esz:] == 0xA5).all()), f"{name}: guard written"
     assert torch.equal(v16, vp.bfloat16())
     assert abs(float(vp.double().norm()) - float(np.linalg.norm(p.astype(np.float64)))) <= 1e-6 * float(np.linalg.norm(p))
+
+
+@pytest.mark.parametrize("rule", ["adam", "adamh"])
+def test_row_blocks_own_rates_norms_and_frozen_rows(rule):
+    """The case of the reference's engine test (tests/s6/test_engine.cpp:416-534) through the one-tensor entry points: a
+    [96, 64] tensor, rows [0, 32) block 0 with learning rate x 0.5, [32, 64) block 1 frozen, [64, 96) block 2; frozen
+    rows keep p, mu, nu; each AdamH block keeps its own Frobenius norm (1e-6); element error against the f64 update
+    within 2e-6; against the oracle's f32 order: Adam bit-equal, AdamH 2e-7."""
+    A = _A()
+    from gpu_common import lib, nmce
+    R, C, t = 96, 64, 1
+    p, g, mu, nu = _state(100, (R, C))
+    mu *= 0.1
+    bor = (np.arange(R) // 32).astype(np.int32)
+    mult = np.array([0.5, 0.5, 1.0], np.float32)
+    frozen = np.array([0, 1, 0], np.uint8)
+    lr = 0.008 if rule == "adam" else 0.02
+    P, G, M, V = (torch.from_numpy(a.copy()).cuda() for a in (p, g, mu, nu))
+    P16 = torch.full((R, C), 7.0, dtype=torch.bfloat16, device="cuda")
+    B, MU, FR = torch.from_numpy(bor).cuda(), torch.from_numpy(mult).cuda(), torch.from_numpy(frozen).cuda()
+    fn = lib().nm_adam_update if rule == "adam" else lib().nm_adamh_update
+    fn(nmce.ptr(P), nmce.ptr(P16), nmce.ptr(G), nmce.ptr(M), nmce.ptr(V), R, C, t, lr, 0.9, 0.98, 1e-20, 0.0, 0, 1.0,
+       nmce.ptr(B), nmce.ptr(MU), nmce.ptr(FR), 3, None)
+    torch.cuda.synchronize()
+    ofn = A.adam_f32 if rule == "adam" else A.adamh_f32
+    p2, mu2, nu2 = A.with_row_blocks(ofn, p, g, mu, nu, t, lr, 0.9, 0.98, 1e-20, bor, mult, frozen)
+    got, gm, gv = P.cpu().numpy(), M.cpu().numpy(), V.cpu().numpy()
+    fr = bor == 1
+    assert np.array_equal(got[fr], p[fr]) and np.array_equal(gm[fr], mu[fr]) and np.array_equal(gv[fr], nu[fr])
+    assert bool((P16[32:64] == 7.0).all()) and torch.equal(P16[:32], P[:32].bfloat16()) and torch.equal(P16[64:], P[64:].bfloat16())
+    assert np.array_equal(gm, mu2) and np.array_equal(gv, nu2)
+    if rule == "adam":
+        assert np.array_equal(got, p2)
+    else:
+        assert np.linalg.norm(got - p2) <= 2e-7 * np.linalg.norm(p2)
+        for blk in (0, 2):
+            rows = bor == blk
+            n0, n1 = np.linalg.norm(p[rows].astype(np.float64)), np.linalg.norm(got[rows].astype(np.float64))
+            assert abs(n1 - n0) <= 1e-6 * n0
+            q2, _, _ = A.adamh_f64(p[rows], g[rows], mu[rows], nu[rows], t, np.float32(lr) * mult[blk], 0.9, 0.98, 1e-20)
+            assert np.abs(got[rows] - q2).max() <= 2e-6 * np.abs(q2).max()

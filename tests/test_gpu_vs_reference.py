@@ -187,3 +187,37 @@ def test_adam_update_against_the_reference_library():
             assert torch.equal(P, RP)
         else:
             assert float((P.double() - RP.double()).norm() / RP.double().norm()) <= 1e-7
+
+
+@pytest.mark.parametrize("rule", ["nm_adam_update", "nm_adamh_update"])
+def test_row_blocks_against_the_reference_library(rule):
+    """Row blocks (own learning-rate multipliers, a frozen block, per-block AdamH norms) through both libraries' one-tensor
+    entry points: moments bit-equal, parameters bit-equal for Adam and within 1e-6 for AdamH."""
+    if not os.path.exists(REF_OPT):
+        pytest.skip("oracle/_ref/libref_optim.so was not built (make -C oracle _ref/libref_optim.so)")
+    import ctypes
+    from gpu_common import lib, nmce
+    rdll = ctypes.CDLL(REF_OPT)
+    getattr(rdll, rule).restype, getattr(rdll, rule).argtypes = nmce.SIGS[rule]
+    rng = np.random.default_rng(11)
+    R, C = 200, 72
+    p = (rng.standard_normal((R, C)) * 0.02).astype(np.float32)
+    g = (rng.standard_normal((R, C)) * 1e-3).astype(np.float32)
+    mu = (rng.standard_normal((R, C)) * 1e-4).astype(np.float32)
+    nu = ((rng.standard_normal((R, C)) * 1e-3) ** 2).astype(np.float32)
+    bor = torch.from_numpy(rng.integers(0, 4, R).astype(np.int32)).cuda()
+    mult = torch.tensor([0.5, 1.0, 2.0, 0.25], dtype=torch.float32, device="cuda")
+    frozen = torch.tensor([0, 0, 1, 0], dtype=torch.uint8, device="cuda")
+    out = []
+    for fn in (lib().raw(rule), getattr(rdll, rule)):
+        P, G, M, V = (torch.from_numpy(a.copy()).cuda() for a in (p, g, mu, nu))
+        assert fn(nmce.ptr(P), None, nmce.ptr(G), nmce.ptr(M), nmce.ptr(V), R, C, 1, 0.01, 0.9, 0.98, 1e-20, 0.0, 0, 1.0,
+                  nmce.ptr(bor), nmce.ptr(mult), nmce.ptr(frozen), 4, None) == 0
+        torch.cuda.synchronize()
+        out.append((P, M, V))
+    (P, M, V), (RP, RM, RV) = out
+    assert torch.equal(M, RM) and torch.equal(V, RV)
+    if rule == "nm_adam_update":
+        assert torch.equal(P, RP)
+    else:
+        assert float((P.double() - RP.double()).norm() / RP.double().norm()) <= 1e-6
