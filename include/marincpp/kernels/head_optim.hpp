@@ -55,7 +55,8 @@ class HeadAdamH {
   // One update. grad: the [V, D] f32 gradient (with a reducer: after its buckets were reduced to their owners; the call
   // waits for the reducer on `st`). p_owned, mu_owned, nu_owned: this rank's master parameters and moments, compact.
   // w16: the [V, D] bf16 replica, rewritten on owned ranges and, with a reducer, all-gathered. Everything runs on `st`;
-  // nothing is allocated and the host is not synchronised.
+  // nothing is allocated and the host is not synchronised. One step at a time per object (its scalars and block
+  // partials live in device memory the object owns); the object belongs to the device that was current when it was made.
   void step(const AdamHStep& s, const float* grad, float* p_owned, float* mu_owned, float* nu_owned, bf16_t* w16,
             cudaStream_t st);
 
