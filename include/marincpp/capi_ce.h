@@ -74,8 +74,9 @@ int nm_ce_suggest_chunk_rows(int64_t T);
 
 /* How many CTAs work on one accumulator tile in the logits, dX and dW contractions: 0 = one CTA per 128 x 256 tile,
  * non-zero = a pair of CTAs on one TPC per 256 x 256 tile (tcgen05 cta_group::2; the B operand is staged once per
- * pair), negative = chosen per launch (the default: pairs for the dX and dW contractions of calls with hidden size up
- * to 512 and at most 16384 rows per chunk, where they were measured to pay; one CTA per tile otherwise). Results are
+ * pair), negative = chosen per launch (the default: pairs where they were measured to pay: the dX and dW contractions
+ * of calls with hidden size up to 512 and at most 16384 rows per chunk, the logits contraction of calls with hidden
+ * size 1024 .. 2048 and at least 4096 rows per chunk; one CTA per tile otherwise). Results are
  * bit-identical between the two forms. Process-wide; call it while no CE call is in flight. No
  * counterpart in the reference (its nm_ce_set_backends chooses between its own kernels and cuBLASLt). */
 int nm_ce_set_cta_pair(int logits, int dgrad, int wgrad);

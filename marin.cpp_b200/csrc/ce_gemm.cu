@@ -688,13 +688,17 @@ void launch(int ncta, const CUtensorMap& ta, const CUtensorMap& tb, const CUtens
 }
 
 // CTAs per tile for the three contractions: 1, 2 (pair mode) or 0 = chosen per launch. Pairs finish a tile in fewer
-// cycles but draw more power, and on the power-capped large shapes the kernels around them lose what the paired
-// kernel gains; measured, they pay for the dX and dW contractions of short, narrow calls (hidden size up to 512, at
-// most 16384 rows per chunk: the per-layer readouts), 2.8 % of that step.
+// cycles but draw more power, and on the power-capped large shapes the kernels around them lose most of what the
+// paired kernel gains. The choice follows interleaved measurements (both forms alternated inside one process):
+//   dX, dW: pairs for short, narrow calls (hidden size up to 512, at most 16384 rows per chunk: the per-layer
+//           readouts), 2.8 % of that step;
+//   logits: pairs for hidden sizes 1024 .. 2048 on calls of at least 4096 rows (step - 1.7 % at 1024, - 0.9 % at
+//           2048); at 512 the kernel is bound by its epilogue and pairs are slower, at 4096 the step got 2 % slower.
 int g_ncta[3] = {0, 0, 0};
 int ncta_for(int which, int rows, int D) {
   if (g_ncta[which] != 0) return g_ncta[which];
-  return (which != 0 && D <= 512 && rows <= 16384) ? 2 : 1;
+  if (which == 0) return (D >= 1024 && D <= 2048 && rows >= 4096) ? 2 : 1;
+  return (D <= 512 && rows <= 16384) ? 2 : 1;
 }
 
 }  // namespace
