@@ -270,6 +270,9 @@ def main():
     ap.add_argument("--buckets", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (small cases for profiling)")
     ap.add_argument("--cta-pair", default="", help="three digits (logits, dX, dW): 1 = a CTA pair per tile, 0 = one CTA, e.g. 011; default: chosen per launch")
+    ap.add_argument("--grad-path", type=int, default=-1,
+                    help="how dX / dW get the normalised gradient: 0 in-place pass + 128x256 tiles, 1 pass + 256x512 pair "
+                         "tiles, 2 formed inside the pair-tile kernels (no pass); -1: chosen per call")
     ap.add_argument("--zero1", action="store_true",
                     help="reduce dW to its owners (reduce-scatter), AdamH on owned elements and all-gather of the bf16 "
                          "head inside every step, instead of the dW all-reduce (the optimizer then is in the timing)")
@@ -299,6 +302,7 @@ def main():
     lib = nmce.Lib()
     if args.cta_pair:
         lib.nm_ce_set_cta_pair(*[int(ch) for ch in args.cta_pair])
+    lib.nm_ce_set_grad_path(args.grad_path)
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -567,7 +571,7 @@ def main():
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD[args.config] + (f" [tokens overridden to {T}]" if args.tokens > 0 else ""),
                    "tokens_per_gpu": R * T, "hidden": D, "vocab": V,
-                   "chunk_rows": chunk, "readouts": R, "parallelism": f"dp{world} (rows sharded, W replicated)",
+                   "chunk_rows": chunk, "readouts": R, "grad_path": args.grad_path, "parallelism": f"dp{world} (rows sharded, W replicated)",
                    "dw_allreduce": ((f"f32 reduce-scatter to owners, {args.buckets} buckets, overlapped with the last dX"
                                      if args.zero1 else
                                      f"{cfg['reduce']}, {args.buckets} buckets, overlapped with the last dX")
@@ -580,7 +584,7 @@ def main():
                    "loss": loss_value},
         "clocks": clocks,
         "e2e": e2e,
-        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches": int(sum(prof_n)) + (launches_per_step - R * n_chunks * 6) * args.steps,
         "roofline": {"bound": "tensor", "kernel": f"k_ce_umma<{dom}>", "achieved": achieved, "peak": pk["sustained"],
                      "unit": "TFLOP/s", "frac": achieved / pk["sustained"], "traffic": traffic,
                      "peak_source": f"{pk['source']} (sustained; burst {pk['burst']})",

@@ -81,25 +81,45 @@ int nm_ce_suggest_chunk_rows(int64_t T);
  * counterpart in the reference (its nm_ce_set_backends chooses between its own kernels and cuBLASLt). */
 int nm_ce_set_cta_pair(int logits, int dgrad, int wgrad);
 
-/* One of the three tcgen05 contractions alone, for unit tests and ncu (kind 0: C[M,N] f32 = A[M,K] B[N,K]^T, both
+/* How the two gradient contractions of a chunk get the normalised gradient n and which tile form they use:
+ * 0 = an in-place pass over the logits store writes n, dX / dW run on 128 x 256 tiles; 1 = the same pass, dX / dW on
+ * CTA pairs with 256 x 512 tiles (one 512-column TMEM accumulator); 2 = no pass: dX / dW read the raw logits and form
+ * n in shared memory ahead of the tensor-core instructions (256 x 512 tiles); -1 = chosen per call (the default: 2 for
+ * hidden sizes up to 512, else 0). Loss, lse and dX are bit-identical across the three; dW differs only by summation
+ * order between tile forms. Calls with an f32 logits store or f32 io always take form 0. Process-wide. No counterpart
+ * in the reference (its nm_ce_set_backends chooses between its own kernels and cuBLASLt). */
+int nm_ce_set_grad_path(int path);
+
+/* One of the tcgen05 contractions alone, for unit tests and ncu (kind 0: C[M,N] f32 = A[M,K] B[N,K]^T, both
  * K-major; 1: C[M,N] f32 = A[M,K] B[K,N], B N-major; 2: C[M,N] f32 = A[K,M]^T B[K,N], both MN-major; kind + 4: the same
- * with CTA pairs). bf16 operands, row-major with leading dimensions in elements; `status` is a device uint32 the
- * kernel ORs its wait errors into. */
+ * with CTA pairs; kind + 8 (kinds 1 and 2): the 256 x 512-tile pair kernel; kind + 8 + 16: that kernel with A holding
+ * raw logits that it turns into a p - b onehot(target) on the fly, `row_factors` being a device array of
+ * {float e, a, b; int32 target} per row of the logits (rows = M for kind 1, K for kind 2), NULL otherwise). bf16
+ * operands, row-major with leading dimensions in elements; `status` is a device uint32 the kernel ORs its wait errors
+ * into. */
 int nm_ce_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int M,
-                    int N, int K, uint32_t* status, void* stream);
+                    int N, int K, uint32_t* status, const void* row_factors, void* stream);
 
 /* Forward only (per-token loss, lse, per-chunk loss sums; bf16 x and W) WITHOUT a caller workspace and without any
  * allocation: the scratch of one chunk lives in a 16 MiB device array built into the library (held by every GPU that
  * loads it). This entry point has no counterpart in the reference. It is for callers that cannot allocate: a trainer
  * whose single up-front arena has no region planned for an extra evaluation or probe call, or a thread that runs while
  * a stream capture is open, when cudaMalloc is not permitted. Same results as nm_fused_linear_ce_ex with
- * forward_only = 1 and the same chunk_rows. Needs 256 + 8 ceil(V / 256) chunk_rows + 12 chunk_rows bytes of scratch
- * (chunk_rows <= 4096 at V = 128256); a larger request returns NM_ERR_INVALID. The first call on a device resolves
+ * forward_only = 1 and the same chunk_rows. With r = min(chunk_rows, T) it needs 256 + 8 ceil(V / 256) r + 4 r bytes
+ * of scratch (r <= 4096 at V = 128256); a larger request returns NM_ERR_INVALID. The first call on a device resolves
  * the array's device address: make it before any stream capture. All calls on a GPU share the array: calls whose
  * kernels may overlap on the device race and must be serialised by the caller. lse and loss_partial may be NULL. */
 int nm_ce_forward_noalloc(const void* x, const void* w, const int32_t* targets, const float* weight, float* loss_tok,
                           float* lse, float* loss_partial, int64_t T, int D, int V, int chunk_rows,
                           float z_loss_weight, int32_t ignore_index, void* stream);
+/* The wait-status word of the calls above on the current device (nm_ce_device_status needs a workspace pointer, which
+ * a caller of nm_ce_forward_noalloc never holds): copies word 0 of the built-in array to *status_host, synchronises
+ * `stream`, and returns NM_ERR_DEVICE when a bit is set (a bounded wait inside a kernel ran out: discard that call's
+ * losses). Allocates nothing. Each nm_ce_forward_noalloc clears the word when it starts, so read it after the call
+ * you care about and before the next one. No counterpart in the reference. */
+int nm_ce_forward_noalloc_status(void* stream, uint32_t* status_host);
+/* Test hook for the line above: points the short wait probe of nm_ce_test_wait_timeout at that status word. */
+int nm_ce_forward_noalloc_test_timeout(int64_t limit_cycles, void* stream);
 
 /* ---- data-parallel dW reduction over NCCL (the role of the reference's include/marincpp/comm.hpp:22-58 GradReducer
  *      and of src/train/trainer.cpp:50,139): one communicator per process (one process per GPU) ------------------- */

@@ -8,28 +8,21 @@
 
 #include <algorithm>
 
+#include "ce_grad_math.cuh"
 #include "ce_internal.hpp"
+#include "ce_umma.cuh"
 #include "ptx.cuh"
 
 namespace nm::ce {
 namespace {
-
-constexpr float kLog2e = 1.4426950408889634f;
-
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
-__device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
-__device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
 // ------------------------------------------------------------------------------------------------ finalize
 // 32 rows per CTA (lane = row), 8 warps: warp w merges the tile partials of segment w of the vocabulary in ascending
 // order (m_w = max_i m_i, s_w = sum_i s_i exp(m_i - m_w)); warp 0 then merges the 8 segments in ascending order:
 // M = max_w m_w (0 when not finite), S = sum_w s_w exp(m_w - M), lse = log S + M. The order depends only on the
 // number of tiles, so lse and the loss do not depend on the chunk size or the launch geometry.
-// loss = lse - z[target] + L lse^2 for a row that counts, else 0. rowb = weight (0 for an ignored target or a
-// forward-only call), rowa = rowb (1 + 2 L lse): the two per-row factors of the normalised gradient.
+// loss = lse - z[target] + L lse^2 for a row that counts, else 0. A gradient call also gets the row's packed factors
+// of the normalised gradient: b = weight (0 for an ignored target), a = b (1 + 2 L lse), e = -lse log2e, the target.
 constexpr int kFinWarps = 8;
 __global__ void __launch_bounds__(32 * kFinWarps) k_ce_finalize_rows(FinalizeArgs p) {
   __shared__ float sm[kFinWarps][32], ss[kFinWarps][32];
@@ -73,9 +66,11 @@ __global__ void __launch_bounds__(32 * kFinWarps) k_ce_finalize_rows(FinalizeArg
   }
   p.lse[r] = lse;
   p.loss_tok[r] = loss;
-  const float rb = (p.grads && valid) ? wt : 0.f;
-  p.rowb[r] = rb;
-  p.rowa[r] = (p.z_loss != 0.f) ? __fmul_rn(rb, __fmaf_rn(2.f * p.z_loss, lse, 1.f)) : rb;
+  if (p.rowf) {
+    const float b = valid ? wt : 0.f;
+    const float a = (p.z_loss != 0.f) ? __fmul_rn(b, __fmaf_rn(2.f * p.z_loss, lse, 1.f)) : b;
+    p.rowf[r] = RowFactors{gradmath::exponent_of(lse), a, b, valid ? tg : -1};
+  }
 }
 
 // sum_t weight[t] * loss[t] by one CTA of 1024 threads: thread-strided sequential f32 sums, then a binary tree. The
@@ -108,71 +103,129 @@ __global__ void __launch_bounds__(1024) k_sum_scale(const float* w, int64_t n, f
 }
 
 // ------------------------------------------------------------------------------------------------ normalised gradient
-// n = rowa p - rowb onehot, p = exp(z_s - lse) = 2^(z_s log2e - lse log2e); columns >= V are written as 0.
-__device__ __forceinline__ float grad_n(float zs, float neg_lse2, float ra, float rb, bool is_target, bool ok) {
-  const float p = nm::ptx::ex2_approx(fmaf(zs, kLog2e, neg_lse2));
-  const float d = __fmul_rn(p, ra);
-  const float r = is_target ? __fsub_rn(d, rb) : d;
-  return ok ? r : 0.f;
+// The stand-alone rewrite of a chunk's logits store as n = a p - b onehot(target) (element math: ce_grad_math.cuh),
+// used when the gradient contractions do not form n themselves (hidden sizes where that costs more than it saves, the
+// f32 store, the f32-io path, and the nm_ce_dlogits entry point; the reference's counterpart is the pass of
+// src/kernels/cross_entropy/ce_logits.cu:262-318).
+//
+// bf16 store: a TMA pipeline. The store is cut into tiles of 32 rows x 256 columns (16 KiB); each persistent CTA walks
+// its tiles through a ring of four shared-memory slots: one thread keeps three tile loads in flight
+// (cp.async.bulk.tensor -> mbarrier), all 256 threads rewrite the landed tile in place in shared memory (four 16-byte
+// pieces each, eight threads side by side on one row so that shared-memory accesses are conflict-free), and the same
+// thread sends the slot back to where it came from with a TMA store; a slot is refilled once the store that last
+// read it has drained. Global traffic is whole 512-byte row segments in both directions and no thread ever waits on
+// its own global load. The tensor map spans the padded row (ldS columns), so the padding columns are written as 0.
+constexpr int kDzTileRows = 32, kDzTileCols = 256, kDzSlots = 4, kDzThreads = 256;
+constexpr int kDzTileBytes = kDzTileRows * kDzTileCols * 2;
+constexpr int kDzSmem = kDzSlots * kDzTileBytes + 128 /*alignment slack*/ + 64 /*barriers*/;
+
+struct RowABE { float e, a, b; int tg; };
+__device__ __forceinline__ RowABE row_factors(const DzArgs& p, int r) {
+  if (r >= p.rows) return RowABE{0.f, 0.f, 0.f, -1};
+  if (p.rowf) {
+    const RowFactors f = p.rowf[r];
+    return RowABE{f.e, f.a, f.b, f.target};
+  }
+  return RowABE{gradmath::exponent_of(p.lse[r]), p.ga[r], p.gb[r], p.targets[r]};
 }
 
-// bf16 store, in place. Each thread owns one 16-byte piece (8 logits) of kDzRows consecutive rows; all loads of a
-// thread are issued before its math, and the grid strides over row groups.
-constexpr int kDzRows = 4;
-__global__ void __launch_bounds__(256) k_ce_dlogits_bf16(DzArgs p) {
-  const int npieces = int((p.V + 7) / 8);
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= npieces) return;
-  const int v0 = c * 8;
-  __nv_bfloat16* base = static_cast<__nv_bfloat16*>(p.store);
-  for (int r0 = blockIdx.y * kDzRows; r0 < p.rows; r0 += gridDim.y * kDzRows) {
-    uint4 raw[kDzRows];
+__global__ void __launch_bounds__(kDzThreads) k_ce_dlogits_tiles(const __grid_constant__ CUtensorMap tm, const DzArgs p,
+                                                                uint32_t* status) {
+  using namespace nm::ptx;
+  extern __shared__ __align__(128) uint8_t dz_smem_raw[];
+  const uint32_t raw = smem_u32(dz_smem_raw);
+  const uint32_t base = (raw + 127u) & ~127u;
+  const uint32_t bar0 = base + kDzSlots * kDzTileBytes;
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  const int col_tiles = int((p.ldS + kDzTileCols - 1) / kDzTileCols);
+  const int row_tiles = (p.rows + kDzTileRows - 1) / kDzTileRows;
+  const int64_t total = int64_t(col_tiles) * row_tiles;
+  const int64_t first = blockIdx.x;
+  const int mine = first < total ? int((total - first + gridDim.x - 1) / gridDim.x) : 0;
+  auto tile_xy = [&](int i, int& c0, int& r0) {
+    const int64_t t = first + int64_t(i) * gridDim.x;
+    c0 = int(t % col_tiles) * kDzTileCols;
+    r0 = int(t / col_tiles) * kDzTileRows;
+  };
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kDzSlots; ++s) mbar_init(bar0 + 8u * s, 1);
+    abort_word = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  auto fetch = [&](int i) {                    // thread 0 only
+    int c0, r0;
+    tile_xy(i, c0, r0);
+    const int s = i % kDzSlots;
+    mbar_arrive_expect_tx(bar0 + 8u * s, kDzTileBytes);
+    tma_load_2d(base + s * kDzTileBytes, &tm, bar0 + 8u * s, c0, r0);
+  };
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tm);
+    for (int i = 0; i < kDzSlots - 1 && i < mine; ++i) fetch(i);
+  }
+  const int trow = threadIdx.x >> 3, tcol = threadIdx.x & 7;
+  for (int i = 0; i < mine; ++i) {
+    const int s = i % kDzSlots;
+    int c0, r0;
+    tile_xy(i, c0, r0);
+    const RowABE f = row_factors(p, r0 + trow);          // issued before the wait: its latency hides behind the tile's
+    if (!mbar_wait<true>(bar0 + 8u * s, uint32_t(i / kDzSlots) & 1u, abort_flag, status, kErrTransformWait)) break;
+    const uint32_t row_addr = base + s * kDzTileBytes + trow * (kDzTileCols * 2);
+    uint4 v[4];
 #pragma unroll
-    for (int q = 0; q < kDzRows; ++q)
-      if (r0 + q < p.rows) raw[q] = *reinterpret_cast<const uint4*>(base + int64_t(r0 + q) * p.ldS + v0);
+    for (int q = 0; q < 4; ++q) v[q] = ld_shared_v4(row_addr + uint32_t(q * 8 + tcol) * 16u);
 #pragma unroll
-    for (int q = 0; q < kDzRows; ++q) {
-      const int r = r0 + q;
-      if (r < p.rows) {
-        const float neg = -p.lse[r] * kLog2e, ra = p.rowa[r], rb = p.rowb[r];
-        const int tg = p.targets[r];
-        uint32_t u[4] = {raw[q].x, raw[q].y, raw[q].z, raw[q].w};
+    for (int q = 0; q < 4; ++q) {
+      const int col = c0 + (q * 8 + tcol) * 8;
+      v[q] = gradmath::piece_bf16(v[q], f.e, f.a, f.b, f.tg - col, p.V - col);
+    }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int v = v0 + 2 * e;
-          const float d0 = grad_n(bf_lo(u[e]), neg, ra, rb, v == tg, v < p.V);
-          const float d1 = grad_n(bf_hi(u[e]), neg, ra, rb, v + 1 == tg, v + 1 < p.V);
-          u[e] = pack2(d0, d1);
-        }
-        *reinterpret_cast<uint4*>(base + int64_t(r) * p.ldS + v0) = make_uint4(u[0], u[1], u[2], u[3]);
+    for (int q = 0; q < 4; ++q) st_shared_v4(row_addr + uint32_t(q * 8 + tcol) * 16u, v[q].x, v[q].y, v[q].z, v[q].w);
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      tma_store_2d(&tm, base + s * kDzTileBytes, c0, r0);
+      bulk_commit();
+      if (i + kDzSlots - 1 < mine) {           // the slot tile i - 1 used: its store is the one before the latest
+        bulk_wait_read<1>();
+        fetch(i + kDzSlots - 1);
       }
     }
+  }
+  if (threadIdx.x == 0) {
+    bulk_wait<0>();
+    if (*abort_flag) __nanosleep(200000);      // an expired wait: let loads in flight land before the CTA leaves
   }
 }
 
 // f32 store: the bf16 result of a row is packed over the first half of the same row (leading dimension 2 ldS in bf16
-// elements). A CTA walks its row 1024 logits at a time in ascending order; the bytes a step writes, [2048 s, 2048 s +
-// 2048), were read as f32 by this or an earlier step, and the barrier between a step's reads and writes orders them.
-__global__ void __launch_bounds__(256) k_ce_dlogits_f32(DzArgs p) {
-  for (int r = blockIdx.x; r < p.rows; r += gridDim.x) {
-    const float* zr = static_cast<const float*>(p.store) + int64_t(r) * p.ldS;
-    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(static_cast<float*>(p.store) + int64_t(r) * p.ldS);
-    const float neg = -p.lse[r] * kLog2e, ra = p.rowa[r], rb = p.rowb[r];
-    const int tg = p.targets[r];
-    for (int s0 = 0; s0 < p.ldS; s0 += 1024) {
-      const int v = s0 + int(threadIdx.x) * 4;
-      float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (v < p.ldS) z = *reinterpret_cast<const float4*>(zr + v);   // ldS % 8 == 0: whole float4s
-      __syncthreads();
-      if (v < p.ldS) {
-        const float d0 = grad_n(z.x, neg, ra, rb, v == tg, v < p.V);
-        const float d1 = grad_n(z.y, neg, ra, rb, v + 1 == tg, v + 1 < p.V);
-        const float d2 = grad_n(z.z, neg, ra, rb, v + 2 == tg, v + 2 < p.V);
-        const float d3 = grad_n(z.w, neg, ra, rb, v + 3 == tg, v + 3 < p.V);
-        *reinterpret_cast<uint2*>(out + v) = make_uint2(pack2(d0, d1), pack2(d2, d3));
+// elements). One warp per row, 512 logits per step in ascending order: all of a step's loads are in registers before
+// any of its stores is issued, and a step's stores (bytes [2 s, 2 s + 1024) of the row) only cover logits of this and
+// earlier steps (bytes below 4 s + 2048), so nothing is overwritten before it has been read.
+__global__ void __launch_bounds__(256) k_ce_dlogits_f32_rows(const DzArgs p) {
+  const int lane = threadIdx.x & 31;
+  const int warps = int(gridDim.x) * (blockDim.x >> 5);
+  for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < p.rows; r += warps) {
+    float* zr = static_cast<float*>(p.store) + int64_t(r) * p.ldS;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(zr);
+    const RowABE f = row_factors(p, r);
+    for (int s0 = 0; s0 < p.ldS; s0 += 512) {
+      float4 z[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int v = s0 + u * 128 + lane * 4;
+        z[u] = v < p.ldS ? *reinterpret_cast<const float4*>(zr + v) : make_float4(0.f, 0.f, 0.f, 0.f);   // ldS % 8 == 0
       }
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int v = s0 + u * 128 + lane * 4;
+        if (v < p.ldS) *reinterpret_cast<uint2*>(out + v) = gradmath::piece_f32(z[u], f.e, f.a, f.b, f.tg - v, p.V - v);
+      }
+      __syncwarp();
     }
-    __syncthreads();
   }
 }
 
@@ -235,17 +288,20 @@ void launch_chunk_loss(const float* loss_tok, const float* weight, int rows, flo
 
 void launch_dlogits_inplace(const DzArgs& a, cudaStream_t st) {
   if (a.rows <= 0) return;
-  // 16-byte vector accesses on every row of the store
+  NM_REQUIRE(a.rowf || (a.lse && a.ga && a.gb && a.targets), "dlogits: per-row factors (packed or as four arrays) needed");
   NM_REQUIRE(reinterpret_cast<uintptr_t>(a.store) % 16 == 0 && a.ldS % 8 == 0,
              "dlogits: the store must be 16-byte aligned with a row pitch that is a multiple of 8 elements");
   if (a.store_f32) {
-    k_ce_dlogits_f32<<<std::min(a.rows, sm_count() * 8), 256, 0, st>>>(a);
+    const int warps_per_cta = 8;
+    const int grid = std::max(1, std::min((a.rows + warps_per_cta - 1) / warps_per_cta, sm_count() * 8));
+    k_ce_dlogits_f32_rows<<<grid, 32 * warps_per_cta, 0, st>>>(a);
   } else {
-    const int npieces = int((a.V + 7) / 8);
-    const int gx = (npieces + 255) / 256;
-    const int groups = (a.rows + kDzRows - 1) / kDzRows;
-    const int gy = std::max(1, std::min(groups, std::max(1, sm_count() * 16 / gx)));
-    k_ce_dlogits_bf16<<<dim3(gx, gy), 256, 0, st>>>(a);
+    // one map for loads and stores: [rows, ldS] bf16, boxes of 32 rows x 256 columns, no swizzle
+    const CUtensorMap tm = make_tmap(a.store, uint64_t(a.ldS), uint64_t(a.rows), a.ldS, kDzTileCols, kDzTileRows, false, 0);
+    const int64_t tiles = ((a.ldS + kDzTileCols - 1) / kDzTileCols) * int64_t((a.rows + kDzTileRows - 1) / kDzTileRows);
+    NM_CUDA(cudaFuncSetAttribute(k_ce_dlogits_tiles, cudaFuncAttributeMaxDynamicSharedMemorySize, kDzSmem));
+    const int grid = int(std::max<int64_t>(1, std::min<int64_t>(tiles, int64_t(sm_count()) * 3)));
+    k_ce_dlogits_tiles<<<grid, kDzThreads, kDzSmem, st>>>(tm, a, a.status);
   }
   NM_CUDA(cudaGetLastError());
 }

@@ -7,7 +7,7 @@
 #include <string>
 #include <vector>
 
-#include "capi_util.hpp"
+#include "abi_guard.hpp"
 #include "marincpp/capi_opt.h"
 #include "marincpp/kernels/head_optim.hpp"
 #include "opt_internal.hpp"
@@ -249,7 +249,7 @@ int nm_adamh_update(float* p, void* p16, const float* g, float* mu, float* nu, i
                     float eta, float b1, float b2, float eps, float clip_gn, int clip, float max_norm,
                     const int32_t* block_of_row, const float* block_lr_mult, const uint8_t* block_frozen, int n_blocks,
                     void* stream) {
-  return nm::capi_call([&] {
+  return nm::abi::guarded([&] {
     nm::adamh_update(p, static_cast<nm::bf16_t*>(p16), g, mu, nu, rows, cols, t, eta, b1, b2, eps, clip_gn, clip != 0,
                      max_norm, S(stream), nm::RowBlocks{block_of_row, block_lr_mult, block_frozen, n_blocks});
   });
@@ -259,14 +259,14 @@ int nm_adam_update(float* p, void* p16, const float* g, float* mu, float* nu, in
                    float adam_lr, float b1, float b2, float eps, float clip_gn, int clip, float max_norm,
                    const int32_t* block_of_row, const float* block_lr_mult, const uint8_t* block_frozen, int n_blocks,
                    void* stream) {
-  return nm::capi_call([&] {
+  return nm::abi::guarded([&] {
     nm::adam_update(p, static_cast<nm::bf16_t*>(p16), g, mu, nu, rows, cols, t, adam_lr, b1, b2, eps, clip_gn,
                     clip != 0, max_norm, S(stream), nm::RowBlocks{block_of_row, block_lr_mult, block_frozen, n_blocks});
   });
 }
 
 int nm_grad_reducer_create_owners(void* comm, float* grad, int V, int D, int n_buckets, void** reducer_out) {
-  return nm::capi_call([&] {
+  return nm::abi::guarded([&] {
     NM_REQUIRE(comm && reducer_out, "nm_grad_reducer_create_owners: comm and reducer_out required");
     *reducer_out =
         new nm::GradReducer(*static_cast<nm::Comm*>(comm), grad, V, D, n_buckets, nm::DType::f32, nullptr, true);
@@ -274,21 +274,21 @@ int nm_grad_reducer_create_owners(void* comm, float* grad, int V, int D, int n_b
 }
 
 int nm_head_adamh_create(int V, int D, void* reducer, void** out) {
-  return nm::capi_call([&] {
+  return nm::abi::guarded([&] {
     NM_REQUIRE(out, "nm_head_adamh_create: out required");
     *out = new nm::HeadAdamH(V, D, static_cast<nm::GradReducer*>(reducer));
   });
 }
 int nm_head_adamh_destroy(void* h) {
-  return nm::capi_call([&] { delete static_cast<nm::HeadAdamH*>(h); });
+  return nm::abi::guarded([&] { delete static_cast<nm::HeadAdamH*>(h); });
 }
 int64_t nm_head_adamh_owned_elems(void* h) {
   int64_t n = 0;
-  return nm::capi_call([&] { n = H(h)->owned_elems(); }) == NM_OK ? n : 0;
+  return nm::abi::guarded([&] { n = H(h)->owned_elems(); }) == NM_OK ? n : 0;
 }
 int nm_head_adamh_ranges(void* h, int cap, int64_t* global_off_host, int64_t* compact_off_host, int64_t* len_host,
                          int* n_out) {
-  return nm::capi_call([&] {
+  return nm::abi::guarded([&] {
     NM_REQUIRE(global_off_host && compact_off_host && len_host && n_out, "nm_head_adamh_ranges: outputs required");
     const int n = H(h)->n_ranges();
     *n_out = n;
@@ -296,12 +296,12 @@ int nm_head_adamh_ranges(void* h, int cap, int64_t* global_off_host, int64_t* co
   });
 }
 int nm_head_adamh_init_master(void* h, const void* w16, float* p_owned, void* stream) {
-  return nm::capi_call([&] { H(h)->init_master(static_cast<const nm::bf16_t*>(w16), p_owned, S(stream)); });
+  return nm::abi::guarded([&] { H(h)->init_master(static_cast<const nm::bf16_t*>(w16), p_owned, S(stream)); });
 }
 int nm_head_adamh_step(void* h, int64_t t, float eta, float b1, float b2, float eps, float max_grad_norm,
                        float grad_scale, const float* grad, float* p_owned, float* mu_owned, float* nu_owned, void* w16,
                        void* stream) {
-  return nm::capi_call([&] {
+  return nm::abi::guarded([&] {
     nm::AdamHStep s;
     s.t = t, s.eta = eta, s.b1 = b1, s.b2 = b2, s.eps = eps, s.max_grad_norm = max_grad_norm, s.grad_scale = grad_scale;
     H(h)->step(s, grad, p_owned, mu_owned, nu_owned, static_cast<nm::bf16_t*>(w16), S(stream));
@@ -310,7 +310,7 @@ int nm_head_adamh_step(void* h, int64_t t, float eta, float b1, float b2, float 
 int nm_head_adamh_step_async(void* h, int64_t t, float eta, float b1, float b2, float eps, float max_grad_norm,
                              float grad_scale, const float* grad, float* p_owned, float* mu_owned, float* nu_owned,
                              void* w16, void* stream) {
-  return nm::capi_call([&] {
+  return nm::abi::guarded([&] {
     nm::AdamHStep s;
     s.t = t, s.eta = eta, s.b1 = b1, s.b2 = b2, s.eps = eps, s.max_grad_norm = max_grad_norm, s.grad_scale = grad_scale;
     s.gather_on_comm_stream = true;
@@ -318,10 +318,10 @@ int nm_head_adamh_step_async(void* h, int64_t t, float eta, float b1, float b2, 
   });
 }
 int nm_head_adamh_wait_params(void* h, void* stream) {
-  return nm::capi_call([&] { H(h)->wait_params(S(stream)); });
+  return nm::abi::guarded([&] { H(h)->wait_params(S(stream)); });
 }
 int nm_head_adamh_scalars(void* h, double* out4_host, void* stream) {
-  return nm::capi_call([&] {
+  return nm::abi::guarded([&] {
     NM_REQUIRE(out4_host, "nm_head_adamh_scalars: output required");
     NM_CUDA(cudaMemcpyAsync(out4_host, H(h)->scalars(), 4 * sizeof(double), cudaMemcpyDeviceToHost, S(stream)));
     NM_CUDA(cudaStreamSynchronize(S(stream)));

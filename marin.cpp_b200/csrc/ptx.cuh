@@ -59,8 +59,25 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t par
   return ok != 0;
 }
 
+// The same test with cluster-scope acquire: for a barrier that threads of the other CTA of a pair arrive on after
+// writing shared memory this CTA's tensor core is about to read.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Error bits a kernel ORs into its status word when a wait runs out (one bit per role).
-constexpr uint32_t kErrProducerWait = 1u, kErrMmaWait = 2u, kErrEpilogueWait = 4u, kErrTmemFreeWait = 8u;
+constexpr uint32_t kErrProducerWait = 1u, kErrMmaWait = 2u, kErrEpilogueWait = 4u, kErrTmemFreeWait = 8u,
+                   kErrTransformWait = 16u;
 
 // Waits for the phase with the given parity, but never forever: after `kWaitCycles` SM clocks (one to two seconds; a
 // correct run waits microseconds) it raises the CTA's abort flag, records `err` in the status word and returns false.
@@ -81,6 +98,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
       }
     }
+    if (*abort_flag) return false;
+    if (clock64() - t0 > limit_cycles) {
+      *abort_flag = 1;
+      if (status) atomicOr(status, err);
+      return false;
+    }
+  }
+}
+
+// The bounded wait with cluster-scope acquire (see mbar_try_wait_cluster).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  uint32_t* status, uint32_t err, long long limit_cycles = kWaitCycles) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > limit_cycles) {
       *abort_flag = 1;
@@ -149,6 +184,11 @@ __device__ __forceinline__ void bulk_wait() {
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
 }
 // 3-D tiled loads (c0 innermost), plain and with an L2 eviction policy.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap, uint32_t bar, int c0, int c1, int c2) {

@@ -37,7 +37,10 @@ SIGS = {
     "nm_ce_test_wait_timeout": (I32, [VP, I64, VP, VP]),
     "nm_ce_set_cta_pair": (I32, [I32, I32, I32]),
     "nm_ce_suggest_chunk_rows": (I32, [I64]),
-    "nm_ce_test_gemm": (I32, [I32, VP, I64, VP, I64, VP, I64, I32, I32, I32, VP, VP]),
+    "nm_ce_test_gemm": (I32, [I32, VP, I64, VP, I64, VP, I64, I32, I32, I32, VP, VP, VP]),
+    "nm_ce_set_grad_path": (I32, [I32]),
+    "nm_ce_forward_noalloc_status": (I32, [VP, VP]),
+    "nm_ce_forward_noalloc_test_timeout": (I32, [I64, VP]),
     "nm_rmsnorm_fwd": (I32, [I32, I32, VP, VP, VP, VP, I64, I32, F32, VP]),
     "nm_norm_partial_rows": (I64, [I64]),
     "nm_rmsnorm_bwd_add_partial": (I32, [I32, I32, VP, VP, VP, VP, VP, VP, VP, I64, I32, F32, VP]),

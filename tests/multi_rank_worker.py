@@ -72,7 +72,9 @@ def main():
     Y = torch.from_numpy(y[sl]).to(dev)
     WT = torch.from_numpy(wt[sl]).to(dev)
     gs = torch.tensor([1.0 / float(wt.sum())], dtype=torch.float32, device=dev)
-    for reduce_dtype, tol in ((0, 1e-5), (1, 8e-3)):
+    # bf16 wire format: every rank's dW is rounded to bf16, summed in bf16 and read back, i.e. two or three bf16
+    # roundings of relative size 2^-9 / sqrt(3) each on top of the f32 result: inside the 3e-3 gradient bar
+    for reduce_dtype, tol in ((0, 1e-5), (1, 3e-3)):
         dw = torch.zeros(V, D, dtype=torch.float32, device=dev)
         staging = torch.empty(V, D, dtype=torch.bfloat16, device=dev) if reduce_dtype else None
         red = ctypes.c_void_p()
