@@ -153,6 +153,16 @@ def cpu_sample(cfg, seconds=12.0, rows0=32):
 
 REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libref_ce.so")
 
+# DRAM bytes (read + write) one launch of each tcgen05 kernel moves per row of its chunk, at vocabulary 128256, from
+# hardware-counter captures of small cases of the same kernels (one kernel, a few launches), which grow in proportion
+# to the rows: {hidden: {kernel: bytes per row}}. None where no capture exists.
+DRAM_BYTES_PER_ROW = {}
+
+
+def dram_traffic_per_launch(kernel, D, V, chunk, grad_path):
+    per_row = DRAM_BYTES_PER_ROW.get((D, V, grad_path), {}).get(kernel)
+    return None if per_row is None else per_row * chunk
+
 
 def reference_arm_gpu(args, cfg):
     """The reference's own fused-CE module (compiled unmodified for sm_100a by oracle/Makefile into oracle/_ref/),
@@ -168,39 +178,54 @@ def reference_arm_gpu(args, cfg):
     dev = torch.device("cuda", 0)
     T, D, V = cfg["T"], cfg["D"], cfg["V"]
     R = cfg["readouts"]
-    chunk = min(args.chunk or 16384, T)          # the reference's callers pass 16384 (tests/s5/bench_ce.py)
     X, W, Y, WT = make_inputs(torch, cfg, 0, dev)
     gs = (1.0 / WT.sum()).float().reshape(1) / R
     dx = torch.empty_like(X)
     dw = torch.zeros(V, D, dtype=torch.float32, device=dev)
     loss = torch.empty(T, dtype=torch.float32, device=dev)
     lse = torch.empty(T, dtype=torch.float32, device=dev)
-    lp = torch.zeros((T + chunk - 1) // chunk, dtype=torch.float32, device=dev)
-    ws = torch.empty(dll.nm_ce_workspace_bytes(1, T, D, V, chunk, 1), dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev)
     sp = ctypes.c_void_p(stream.cuda_stream)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    # chunk sizes: the one passed; else both the value the reference's own callers use (16384, tests/s5/bench_ce.py)
+    # and the one the other arm of this bench runs by default (128 x SM count): the faster of the two is reported
+    chunks = [min(args.chunk, T)] if args.chunk else sorted({min(16384, T), min(128 * sms, T)})
 
-    def step():
-        dw.zero_()
-        for _ in range(R):
-            r = dll.nm_fused_linear_ce(1, 0, 1, 1, nmce.ptr(X), nmce.ptr(W), nmce.ptr(Y), nmce.ptr(WT), nmce.ptr(gs),
-                                       None, nmce.ptr(loss), nmce.ptr(lse), nmce.ptr(lp), nmce.ptr(dx), 0, nmce.ptr(dw),
-                                       None, 0, 0, T, D, V, chunk, nmce.ptr(ws), sp)
-            if r != 0:
-                raise RuntimeError("reference nm_fused_linear_ce: " + dll.nm_last_error().decode())
-    for _ in range(max(1, args.warmup)):
-        step()
-    torch.cuda.synchronize(dev)
+    def run(chunk, warmup, steps):
+        lp = torch.zeros((T + chunk - 1) // chunk, dtype=torch.float32, device=dev)
+        ws = torch.empty(dll.nm_ce_workspace_bytes(1, T, D, V, chunk, 1), dtype=torch.uint8, device=dev)
+
+        def step():
+            dw.zero_()
+            for _ in range(R):
+                r = dll.nm_fused_linear_ce(1, 0, 1, 1, nmce.ptr(X), nmce.ptr(W), nmce.ptr(Y), nmce.ptr(WT),
+                                           nmce.ptr(gs), None, nmce.ptr(loss), nmce.ptr(lse), nmce.ptr(lp), nmce.ptr(dx),
+                                           0, nmce.ptr(dw), None, 0, 0, T, D, V, chunk, nmce.ptr(ws), sp)
+                if r != 0:
+                    raise RuntimeError("reference nm_fused_linear_ce: " + dll.nm_last_error().decode())
+        for _ in range(max(1, warmup)):
+            step()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            step()
+        e1.record(stream)
+        torch.cuda.synchronize(dev)
+        del ws
+        return e0.elapsed_time(e1)
+
+    tried = {}
+    if len(chunks) > 1:                       # a short look at each, then the full measurement on the faster one
+        for c in chunks:
+            tried[str(c)] = run(c, 2, 3) / 3
+        chunk = int(min(tried, key=tried.get))
+    else:
+        chunk = chunks[0]
     sampler = ClockSampler(0)
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    torch.cuda.synchronize(dev)
+    ms = run(chunk, args.warmup, args.steps)
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1)
     val = R * T * args.steps / (ms * 1e-3)
     sample = ("GPU run, not CPU: the reference has no CPU implementation of this path; this is its own CE module "
               "(B1, bf16 store, cuBLASLt + mma.sync) built unmodified for sm_100a, full configuration, one GPU")
@@ -209,8 +234,10 @@ def reference_arm_gpu(args, cfg):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD[args.config], "tokens_per_gpu": R * T, "hidden": D, "vocab": V,
-                   "chunk_rows": chunk, "note": "rank 0 only: the reference's CE module on one GPU (its trainer's "
-                   "multi-GPU loop is not part of this path)",
+                   "chunk_rows": chunk, "chunk_rows_tried_ms_per_step": tried or None,
+                   "z_loss": "unsupported by the reference API (its fused CE has no z-loss term): run without it",
+                   "note": "rank 0 only: the reference's CE module on one GPU (its trainer's multi-GPU loop is not "
+                           "part of this path); per-GPU throughput, to be compared with the other arm's value / n_gpus",
                    "path_tflops": 6.0 * R * T * D * V / (ms / args.steps * 1e-3) / 1e12},
         "clocks": clocks,
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": 0, "kind": "reference", "sample": sample},
@@ -259,55 +286,10 @@ def reference_arm(args, cfg, rank, world):
     }))
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--chunk", type=int, default=0, help="chunk rows; 0 = nm_ce_suggest_chunk_rows (128 x SM count)")
-    ap.add_argument("--buckets", type=int, default=8)
-    ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (small cases for profiling)")
-    ap.add_argument("--cta-pair", default="", help="three digits (logits, dX, dW): 1 = a CTA pair per tile, 0 = one CTA, e.g. 011; default: chosen per launch")
-    ap.add_argument("--grad-path", type=int, default=-1,
-                    help="how dX / dW get the normalised gradient: 0 in-place pass + 128x256 tiles, 1 pass + 256x512 pair "
-                         "tiles, 2 formed inside the pair-tile kernels (no pass); -1: chosen per call")
-    ap.add_argument("--zero1", action="store_true",
-                    help="reduce dW to its owners (reduce-scatter), AdamH on owned elements and all-gather of the bf16 "
-                         "head inside every step, instead of the dW all-reduce (the optimizer then is in the timing)")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg")
-    args = ap.parse_args()
-    cfg = dict(CONFIGS[args.config])
-    if args.tokens > 0:
-        cfg["T"] = args.tokens
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.warmup < 3:
-        args.warmup = 3 if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
-        reference_arm(args, cfg, rank, world)
-        return
-
-    os.environ["NCCL_DEBUG"] = os.environ.get("NM_BENCH_NCCL_DEBUG", "NONE")   # NCCL prints its version banner to stdout at any other level: keep stdout to the one JSON line
-    import torch
-    import nmce
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    lib = nmce.Lib()
-    if args.cta_pair:
-        lib.nm_ce_set_cta_pair(*[int(ch) for ch in args.cta_pair])
-    lib.nm_ce_set_grad_path(args.grad_path)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+def measure(args, cfg, name, env, steps, warmup, with_e2e):
+    """One configuration on this rank's GPU: device-resident timing (+ the host-input leg when asked). Returns a dict of
+    raw numbers; every rank calls it, the collectives inside need all of them."""
+    torch, nmce, lib, dist, rank, world, dev = (env[k] for k in ("torch", "nmce", "lib", "dist", "rank", "world", "dev"))
     T, D, V, L = cfg["T"], cfg["D"], cfg["V"], cfg["z_loss"]
     R = cfg["readouts"]
     chunk = min(args.chunk or int(lib.nm_ce_suggest_chunk_rows(T)), T)
@@ -330,16 +312,8 @@ def main():
     stream = torch.cuda.current_stream(dev)
     sp = ctypes.c_void_p(stream.cuda_stream)
 
-    comm = reducer = staging = None
+    comm, reducer, staging = env.get("comm"), None, None
     if world > 1:
-        idbuf = torch.zeros(128, dtype=torch.uint8)
-        if rank == 0:
-            lib.nm_comm_unique_id(nmce.ptr(idbuf))
-        idg = idbuf.to(dev)
-        dist.broadcast(idg, 0)
-        idbuf = idg.cpu()
-        comm = ctypes.c_void_p()
-        lib.nm_comm_create(nmce.ptr(idbuf), world, rank, ctypes.byref(comm))
         if cfg["reduce"] == "bf16":
             staging = torch.empty(V, D, dtype=torch.bfloat16, device=dev)
         reducer = ctypes.c_void_p()
@@ -378,6 +352,15 @@ def main():
                           nmce.ptr(y_in), nmce.ptr(wt_in), nmce.ptr(loss), nmce.ptr(lse), nmce.ptr(lp[r]), 0, T, D, V,
                           chunk, 1e-5, nmce.ptr(ws), sp)
 
+    comm_events = None       # pairs of events around the wait for the dW all-reduce (its exposed, non-overlapped part)
+    other_launches = [0]     # launches per step outside the six timed kernel classes (norms, casts, optimizer)
+    if R > 1:
+        other_launches[0] += R * 2                         # the readout's RMSNorm forward and backward
+    if reducer and cfg["reduce"] == "bf16":
+        other_launches[0] += 2 * args.buckets              # casts around the bf16 all-reduce
+    if args.zero1:
+        other_launches[0] += 5                             # AdamH: clip norm + its partial sum, moments + sums, apply
+
     def step(inputs=None):
         """zero dW, every readout's fused CE (dW accumulates), the dW all-reduce overlapped with the last dX (one
         readout) or issued once after the last readout (pls)."""
@@ -405,8 +388,6 @@ def main():
             lib.nm_head_adamh_step(head_opt, opt_t[0], 1e-6, 0.9, 0.98, 1e-20, 1.0, 1.0, nmce.ptr(dw), nmce.ptr(p_own),
                                    nmce.ptr(mu_own), nmce.ptr(nu_own), nmce.ptr(W), sp)
 
-    comm_events = None       # pairs of events around the wait for the dW all-reduce (its exposed, non-overlapped part)
-
     def barrier():
         if dist:
             dist.barrier()
@@ -416,29 +397,19 @@ def main():
         st = ctypes.c_uint32(0)
         lib.nm_ce_device_status(nmce.ptr(ws), sp, ctypes.byref(st))
 
-    launches_per_step = R * (n_chunks * 6)                 # logits, finalize, dlogits, dW, dX, chunk loss per chunk
-    if R > 1:
-        launches_per_step += R * 2                         # the readout's RMSNorm forward and backward
-    if reducer and R == 1:                                 # the last chunk's dW runs per bucket
-        launches_per_step += args.buckets - 1
-    if reducer and cfg["reduce"] == "bf16":
-        launches_per_step += 2 * args.buckets              # casts around the bf16 all-reduce
-    if args.zero1:
-        launches_per_step += 5                             # AdamH: clip norm + its partial sum, moments + partial sums, apply
-
     # ---------------------------------------------------------------- device-resident timing (value)
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     check_status()
-    lib.nm_ce_profile_enable(launches_per_step * args.steps + 64)
-    sampler = ClockSampler(local_rank)
+    lib.nm_ce_profile_enable(R * (n_chunks * 6 + args.buckets) * steps + 64)
+    sampler = ClockSampler(env["local_rank"])
     barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     comm_events = [] if reducer else None
     e0.record(stream)
     step_marks = []
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
         m = torch.cuda.Event(enable_timing=True)
         m.record(stream)
@@ -451,18 +422,20 @@ def main():
     exposed_comm_ms = None
     if comm_events:
         exposed_comm_ms = sum(comm_events[i].elapsed_time(comm_events[i + 1])
-                              for i in range(0, len(comm_events), 2)) / args.steps
+                              for i in range(0, len(comm_events), 2)) / steps
     comm_events = None
     ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    exposed_by_rank = None
+    exposed_by_rank = clocks_by_rank = None
     if dist:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        # every rank's wait for the all-reduce: the ranks' GPUs run at different power-capped clocks, and the faster
-        # ones wait here for the slowest one's last bucket (the smallest wait is what the collective itself exposes)
-        ex = torch.tensor([exposed_comm_ms or 0.0], dtype=torch.float64, device=dev)
+        # every rank's wait for the all-reduce beside its clock: the ranks' GPUs run at different power-capped clocks,
+        # and the faster ones wait here for the slowest one's last bucket (the smallest wait is what the collective
+        # itself exposes)
+        ex = torch.tensor([exposed_comm_ms or 0.0, float(clocks.get("sm_mhz") or 0.0)], dtype=torch.float64, device=dev)
         allex = [torch.zeros_like(ex) for _ in range(world)]
         dist.all_gather(allex, ex)
-        exposed_by_rank = [round(float(t.item()), 3) for t in allex]
+        exposed_by_rank = [round(float(t[0].item()), 3) for t in allex]
+        clocks_by_rank = [float(t[1].item()) for t in allex]
     ms_total = float(ms.item())
     prof_ms = (ctypes.c_double * 6)()
     prof_n = (ctypes.c_int * 6)()
@@ -476,7 +449,7 @@ def main():
 
     # ---------------------------------------------------------------- host-input timing (e2e)
     e2e = None
-    if not args.no_e2e:
+    if with_e2e:
         hx = [torch.empty(T, D, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
         hy = [torch.empty(T, dtype=torch.int32).pin_memory() for _ in range(2)]
         hw = [torch.empty(T, dtype=torch.float32).pin_memory() for _ in range(2)]
@@ -514,11 +487,11 @@ def main():
                 hlp.copy_(lp, non_blocking=True)        # the step's result: per-chunk weighted losses
             stream.synchronize()
 
-        e2e_steps(args.warmup)
+        e2e_steps(warmup)
         barrier()
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record(stream)
-        e2e_steps(args.steps)
+        e2e_steps(steps)
         f1.record(stream)
         barrier()
         ms2 = torch.tensor([f0.elapsed_time(f1)], dtype=torch.float64, device=dev)
@@ -526,9 +499,179 @@ def main():
             dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
         check_status()
         h2d = T * D * 2 + T * 4 + T * 4                  # one upload of x, targets, weights per step
-        e2e = {"value": world * R * T * args.steps / (float(ms2.item()) * 1e-3), "unit": "tokens/s",
+        e2e = {"value": world * R * T * steps / (float(ms2.item()) * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": R * n_chunks * 4,
-               "ms_per_step": float(ms2.item()) / args.steps}
+               "ms_per_step": float(ms2.item()) / steps}
+
+    if head_opt:
+        lib.nm_head_adamh_destroy(head_opt)
+    if reducer:
+        lib.nm_grad_reducer_destroy(reducer)
+    pk = peaks()
+    names = ["logits", "finalize", "dlogits", "dw", "dx", "chunk_loss"]
+    per_class = {names[i]: {"ms_per_step": prof_ms[i] / steps, "launches_per_step": prof_n[i] / steps}
+                 for i in range(6)}
+    ms_step = ms_total / steps
+    path_tflops = 6.0 * R * T * D * V / (ms_step * 1e-3) / 1e12
+    return dict(name=name, T=T, D=D, V=V, R=R, chunk=chunk, n_chunks=n_chunks, ms_total=ms_total, ms_step=ms_step,
+                per_step=per_step, clocks=clocks, clocks_by_rank=clocks_by_rank, exposed_comm_ms=exposed_comm_ms,
+                exposed_by_rank=exposed_by_rank, prof_ms=list(prof_ms), prof_n=list(prof_n), per_class=per_class,
+                loss=loss_value, e2e=e2e, launches=int(sum(prof_n)) + other_launches[0] * steps,
+                path_tflops=path_tflops, path_frac=path_tflops / pk["sustained"],
+                path_frac_of_burst=path_tflops / pk["burst"], tokens_per_s=world * R * T * steps / (ms_total * 1e-3))
+
+
+def adjacent_kernels(env, tokens=65536, hidden=2048):
+    """The memory-bound kernels on either side of the fused CE (RMSNorm pair, sandwich tail, the in-place gradient
+    pass, the head's AdamH), each timed alone over operands larger than L2: GB/s of algorithmic bytes (every operand read
+    or written once) and the fraction of the measured HBM copy rate. 3 warm-up + 10 timed launches, CUDA events."""
+    torch, nmce, lib = env["torch"], env["nmce"], env["lib"]
+    peak = peaks()["hbm"]
+    T, D = tokens, hidden
+    g = torch.Generator(device="cuda").manual_seed(1)
+    bf = torch.bfloat16
+    x = torch.randn(T, D, generator=g, device="cuda").to(bf)
+    b = torch.randn(T, D, generator=g, device="cuda").to(bf)
+    dy = (torch.randn(T, D, generator=g, device="cuda") * 1e-2).to(bf)
+    gain = torch.ones(D, dtype=bf, device="cuda")
+    y, y2, y3 = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+    rstd, rstd2 = torch.empty(T, device="cuda"), torch.empty(T, device="cuda")
+    P = int(lib.nm_norm_partial_rows(T))
+    part = torch.zeros(2 * P, D, device="cuda")
+    p = nmce.ptr
+    out = {}
+
+    def timed(name, nbytes, fn, n=10, w=3):
+        for _ in range(w):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 4), "gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 3)}
+
+    TD2 = T * D * 2
+    timed("rmsnorm_fwd", 2 * TD2, lambda: lib.nm_rmsnorm_fwd(1, 0, p(x), p(gain), p(y), p(rstd), T, D, 1e-5, None))
+    timed("rmsnorm_bwd_add_partial", 4 * TD2,
+          lambda: lib.nm_rmsnorm_bwd_add_partial(1, 0, p(dy), p(x), p(gain), p(rstd), p(b), p(y2), p(part), T, D, 1e-5,
+                                                 None))
+    timed("sandwich_tail_fwd", 4 * TD2,
+          lambda: lib.nm_sandwich_tail_fwd(1, 0, p(b), p(x), p(gain), p(gain), p(y), p(y2), p(rstd), p(rstd2), T, D,
+                                           1e-5, None))
+    timed("sandwich_tail_bwd", 6 * TD2,
+          lambda: lib.nm_sandwich_tail_bwd(1, 0, p(dy), p(dy), p(y), p(gain), p(rstd2), p(b), p(gain), p(rstd), p(y3),
+                                           p(y2), None, None, T, D, 1e-5, None))
+    V, Rr = 128256, 4096
+    store = torch.randn(Rr, V, generator=g, device="cuda").to(bf)
+    lse = torch.full((Rr,), 12.0, device="cuda")
+    gsc = torch.ones(Rr, device="cuda")
+    tgt = torch.randint(0, V, (Rr,), generator=g, device="cuda", dtype=torch.int32)
+    timed("ce_dlogits_inplace", 4 * Rr * V, lambda: lib.nm_ce_dlogits(1, p(store), V, p(lse), p(gsc), p(tgt), Rr, V, None))
+    del store
+    rows = V // 4
+    P_ = torch.randn(rows, D, generator=g, device="cuda") * 0.02
+    G_ = torch.randn(rows, D, generator=g, device="cuda") * 1e-4
+    M_, V_ = torch.zeros(rows, D, device="cuda"), torch.zeros(rows, D, device="cuda")
+    W_ = torch.empty(rows, D, dtype=bf, device="cuda")
+    h = ctypes.c_void_p()
+    lib.nm_head_adamh_create(rows, D, None, ctypes.byref(h))
+    t_opt = [0]
+
+    def one():
+        t_opt[0] += 1
+        lib.nm_head_adamh_step(h, t_opt[0], 0.02, 0.9, 0.98, 1e-20, 1.0, 1.0, p(G_), p(P_), p(M_), p(V_), p(W_), None)
+    timed("head_adamh_step", 46 * rows * D, one)     # 24 + 18 bytes per element in two passes + 4 for the clip norm
+    lib.nm_head_adamh_destroy(h)
+    out["shape"] = f"{T} x {D} bf16 (dlogits {Rr} x {V}; AdamH {rows} x {D} f32)"
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--chunk", type=int, default=0, help="chunk rows; 0 = nm_ce_suggest_chunk_rows (128 x SM count)")
+    ap.add_argument("--buckets", type=int, default=8)
+    ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (small cases for profiling)")
+    ap.add_argument("--cta-pair", default="", help="three digits (logits, dX, dW): 1 = a CTA pair per tile, 0 = one CTA, e.g. 011; default: chosen per launch")
+    ap.add_argument("--grad-path", type=int, default=-1,
+                    help="how dX / dW get the normalised gradient: 0 in-place pass + 128x256 tiles, 1 pass + 256x512 pair "
+                         "tiles, 2 formed inside the pair-tile kernels (no pass); -1: chosen per call")
+    ap.add_argument("--zero1", action="store_true",
+                    help="reduce dW to its owners (reduce-scatter), AdamH on owned elements and all-gather of the bf16 "
+                         "head inside every step, instead of the dW all-reduce (the optimizer then is in the timing)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg")
+    ap.add_argument("--no-others", action="store_true",
+                    help="skip the short runs of the other configurations and of the neighbouring memory-bound kernels")
+    args = ap.parse_args()
+    cfg = dict(CONFIGS[args.config])
+    if args.tokens > 0:
+        cfg["T"] = args.tokens
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.warmup < 3:
+        args.warmup = 3 if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        reference_arm(args, cfg, rank, world)
+        return
+
+    # stdout carries the one JSON line: whatever NCCL is asked to log goes to stderr unless a file was named
+    if os.environ.get("NCCL_DEBUG") and not os.environ.get("NCCL_DEBUG_FILE"):
+        os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"
+    import torch
+    import nmce
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    lib = nmce.Lib()
+    if args.cta_pair:
+        lib.nm_ce_set_cta_pair(*[int(ch) for ch in args.cta_pair])
+    lib.nm_ce_set_grad_path(args.grad_path)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    env = dict(torch=torch, nmce=nmce, lib=lib, dist=dist, rank=rank, world=world, dev=dev, local_rank=local_rank)
+    if world > 1:
+        idbuf = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            lib.nm_comm_unique_id(nmce.ptr(idbuf))
+        idg = idbuf.to(dev)
+        dist.broadcast(idg, 0)
+        idbuf = idg.cpu()
+        comm = ctypes.c_void_p()
+        lib.nm_comm_create(nmce.ptr(idbuf), world, rank, ctypes.byref(comm))
+        env["comm"] = comm
+
+    m = measure(args, cfg, args.config, env, args.steps, args.warmup, not args.no_e2e)
+
+    # the other configurations, three timed steps each, and the memory-bound neighbours: one GPU, default run only
+    others = adjacent = None
+    if world == 1 and not args.no_others and args.tokens == 0:
+        others = {}
+        for name in sorted(CONFIGS):
+            if name == args.config:
+                continue
+            o = measure(args, dict(CONFIGS[name]), name, env, 3, 3, False)
+            others[name] = {"ms_per_step": o["ms_step"], "tokens_per_s": o["tokens_per_s"], "chunk_rows": o["chunk"],
+                            "path_tflops": o["path_tflops"], "path_frac": o["path_frac"],
+                            "path_frac_of_burst": o["path_frac_of_burst"], "sm_mhz": o["clocks"].get("sm_mhz"),
+                            "per_kernel_class": o["per_class"], "loss": o["loss"]}
+            del o
+            torch.cuda.empty_cache()
+        adjacent = adjacent_kernels(env)
 
     # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1)
     cpu = None
@@ -537,61 +680,56 @@ def main():
         cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
                "sample": f"first {n} rows of the batch, full vocabulary, {secs:.1f} s (cost is linear in rows)"}
 
-    if head_opt:
-        lib.nm_head_adamh_destroy(head_opt)
-    if reducer:
-        lib.nm_grad_reducer_destroy(reducer)
-        lib.nm_comm_destroy(comm)
+    if world > 1:
+        lib.nm_comm_destroy(env["comm"])
     if dist:
         dist.barrier()
         dist.destroy_process_group()
     if rank != 0:
         return
     pk = peaks()
-    tokens = world * R * T * args.steps
-    ms_step = ms_total / args.steps
-    flop_step = 6.0 * R * T * D * V                                  # per GPU
-    path_tflops = flop_step / (ms_step * 1e-3) / 1e12
+    T, D, V, R, chunk = m["T"], m["D"], m["V"], m["R"], m["chunk"]
     names = ["logits", "finalize", "dlogits", "dw", "dx", "chunk_loss"]
-    per_class = {names[i]: {"ms_per_step": prof_ms[i] / args.steps, "launches_per_step": prof_n[i] / args.steps}
-                 for i in range(6)}
-    gemm = {k: per_class[k]["ms_per_step"] for k in ("logits", "dw", "dx")}
+    gemm = {k: m["per_class"][k]["ms_per_step"] for k in ("logits", "dw", "dx")}
     dom = max(gemm, key=gemm.get)
-    dom_launch_ms = prof_ms[names.index(dom)] / max(1, prof_n[names.index(dom)])
-    dom_flop_launch = 2.0 * R * T * D * V * args.steps / max(1, prof_n[names.index(dom)])
+    di = names.index(dom)
+    dom_launch_ms = m["prof_ms"][di] / max(1, m["prof_n"][di])
+    dom_flop_launch = 2.0 * R * T * D * V * args.steps / max(1, m["prof_n"][di])
     achieved = dom_flop_launch / (dom_launch_ms * 1e-3) / 1e12
-    # DRAM bytes per launch of each tcgen05 kernel at hidden 2048 x vocab 128256, from ncu captures of this bench
-    # (dram__bytes_read.sum + dram__bytes_write.sum; summaries under profiles/); unknown for other shapes
-    traffic = {(2048, 128256, 18944): {"logits": 7.60e9, "dw": 11.34e9, "dx": 9.26e9},
-               (2048, 128256, 16384): {"logits": 6.40e9, "dw": 10.07e9, "dx": 8.04e9}}.get((D, V, chunk), {}).get(dom)
     out = {
-        "metric": "fused_ce_fwd_bwd_tokens_per_s", "value": tokens / (ms_total * 1e-3), "unit": "tokens/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-        "ms_per_step_median_rank0": sorted(per_step)[len(per_step) // 2], "ms_per_step_min_rank0": min(per_step),
+        "metric": "fused_ce_fwd_bwd_tokens_per_s", "value": m["tokens_per_s"], "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": m["ms_step"],
+        "ms_per_step_median_rank0": sorted(m["per_step"])[len(m["per_step"]) // 2],
+        "ms_per_step_min_rank0": min(m["per_step"]),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD[args.config] + (f" [tokens overridden to {T}]" if args.tokens > 0 else ""),
                    "tokens_per_gpu": R * T, "hidden": D, "vocab": V,
-                   "chunk_rows": chunk, "readouts": R, "grad_path": args.grad_path, "parallelism": f"dp{world} (rows sharded, W replicated)",
+                   "chunk_rows": chunk, "readouts": R, "grad_path": args.grad_path,
+                   "parallelism": f"dp{world} (rows sharded, W replicated)",
                    "dw_allreduce": ((f"f32 reduce-scatter to owners, {args.buckets} buckets, overlapped with the last dX"
                                      if args.zero1 else
                                      f"{cfg['reduce']}, {args.buckets} buckets, overlapped with the last dX")
                                     if world > 1 else "none (1 GPU)"),
                    "optimizer_in_step": ("AdamH of the head on owned elements + bf16 all-gather (ZeRO-1)"
                                          if args.zero1 else None),
-                   "exposed_allreduce_ms_per_step_rank0": exposed_comm_ms,
-                   "allreduce_wait_ms_per_step_by_rank": exposed_by_rank,
+                   "exposed_allreduce_ms_per_step_rank0": m["exposed_comm_ms"],
+                   "allreduce_wait_ms_per_step_by_rank": m["exposed_by_rank"],
+                   "sm_mhz_median_by_rank": m["clocks_by_rank"],
                    "l2": "inputs (x, W, logits store: > 5 GB per step) exceed the 126 MB L2; no flush needed",
-                   "loss": loss_value},
-        "clocks": clocks,
-        "e2e": e2e,
-        "gpu_launches": int(sum(prof_n)) + (launches_per_step - R * n_chunks * 6) * args.steps,
-        "roofline": {"bound": "tensor", "kernel": f"k_ce_umma<{dom}>", "achieved": achieved, "peak": pk["sustained"],
-                     "unit": "TFLOP/s", "frac": achieved / pk["sustained"], "traffic": traffic,
+                   "loss": m["loss"]},
+        "clocks": m["clocks"],
+        "e2e": m["e2e"],
+        "gpu_launches": m["launches"],
+        "roofline": {"bound": "tensor", "kernel": f"k_ce_{dom}", "achieved": achieved, "peak": pk["sustained"],
+                     "unit": "TFLOP/s", "frac": achieved / pk["sustained"],
+                     "traffic": dram_traffic_per_launch(dom, D, V, chunk, args.grad_path),
                      "peak_source": f"{pk['source']} (sustained; burst {pk['burst']})",
                      "frac_of_burst": achieved / pk["burst"], "launch_ms": dom_launch_ms,
-                     "path_tflops": path_tflops, "path_frac": path_tflops / pk["sustained"],
-                     "path_frac_of_burst": path_tflops / pk["burst"], "per_kernel_class": per_class},
+                     "path_tflops": m["path_tflops"], "path_frac": m["path_frac"],
+                     "path_frac_of_burst": m["path_frac_of_burst"], "per_kernel_class": m["per_class"]},
         "cpu_baseline": cpu,
+        "other_configs": others,
+        "adjacent": adjacent,
     }
     print(json.dumps(out))
 

@@ -55,6 +55,54 @@ __device__ __forceinline__ uint4 piece_bf16(uint4 raw, float e, float a, float b
                     pack_bf16x2(d[6], d[7]));
 }
 
+// The same without a target and with all eight columns present: what nearly every piece of a store is.
+__device__ __forceinline__ uint4 piece_bf16_plain(uint4 raw, float e, float a) {
+  uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int q = 0; q < 4; ++q) u[q] = pack_bf16x2(scaled_p(lo_of(u[q]), e, a), scaled_p(hi_of(u[q]), e, a));
+  return make_uint4(u[0], u[1], u[2], u[3]);
+}
+
+// Two logits at once on the packed f32x2 pipe (two independent, individually rounded operations per instruction: the
+// same bits as the scalar form). ll, ee, aa hold (log2e, log2e), (e, e), (a, a).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint32_t scaled_p_pair(uint32_t two_bf16, uint64_t ll, uint64_t ee, uint64_t aa) {
+  float x0, x1;
+  asm("{\n\t"
+      ".reg .b64 t;\n\t"
+      "mov.b64 t, {%2, %3};\n\t"
+      "fma.rn.f32x2 t, t, %4, %5;\n\t"
+      "mov.b64 {%0, %1}, t;\n\t"
+      "}"
+      : "=f"(x0), "=f"(x1)
+      : "f"(lo_of(two_bf16)), "f"(hi_of(two_bf16)), "l"(ll), "l"(ee));
+  const float p0 = nm::ptx::ex2_approx(x0), p1 = nm::ptx::ex2_approx(x1);
+  float d0, d1;
+  asm("{\n\t"
+      ".reg .b64 t;\n\t"
+      "mov.b64 t, {%2, %3};\n\t"
+      "mul.rn.f32x2 t, t, %4;\n\t"
+      "mov.b64 {%0, %1}, t;\n\t"
+      "}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(p0), "f"(p1), "l"(aa));
+  return pack_bf16x2(d0, d1);
+}
+__device__ __forceinline__ uint4 piece_bf16_plain2(uint4 raw, uint64_t ll, uint64_t ee, uint64_t aa) {
+  return make_uint4(scaled_p_pair(raw.x, ll, ee, aa), scaled_p_pair(raw.y, ll, ee, aa), scaled_p_pair(raw.z, ll, ee, aa),
+                    scaled_p_pair(raw.w, ll, ee, aa));
+}
+
+// The one element of a row that holds its target: bf16(a p - b), as a 16-bit pattern.
+__device__ __forceinline__ uint16_t target_element(uint16_t raw, float e, float a, float b) {
+  const float d = __fsub_rn(scaled_p(__uint_as_float(uint32_t(raw) << 16), e, a), b);
+  return __bfloat16_as_ushort(__float2bfloat16_rn(d));
+}
+
 // Four consecutive f32 logits -> four bf16 values of n (the f32 store).
 __device__ __forceinline__ uint2 piece_f32(float4 z, float e, float a, float b, int hit, int nvalid) {
   float d[4] = {scaled_p(z.x, e, a), scaled_p(z.y, e, a), scaled_p(z.z, e, a), scaled_p(z.w, e, a)};

@@ -21,12 +21,18 @@
 //     that share A (the N tiles of a wide hidden size) simply transform it again.
 //   * Plain form: A is already n (the in-place pass ran); the warps 2-9 idle until the epilogue.
 //
-// Warp roles per CTA (320 threads): warp 0 TMA producer (one lane), warp 1 TMEM allocation + UMMA issue (one lane, leader
-// CTA only), warps 2-9 transform + epilogue. Barriers per stage: full_a (this CTA's A bytes, fused form), full_b (leader:
-// B bytes of both CTAs, plus A bytes in the plain form), xformed (leader: 16 warp arrivals), empty (UMMAs have read the
-// stage: commit multicast to both CTAs). No TMA load is multicast. Every wait is bounded.
+// Warp roles per CTA (576 threads): warp 0 TMA producer (one lane), warp 1 TMEM allocation + UMMA issue (one lane, leader
+// CTA only; in the other CTA that lane is the relay), warps 2-17 transform (four per scheduler: with two, the dependent
+// chain load - exponential - pack - store left the issue slots 70 % idle and the tensor pipe at 65 %), of which warps
+// 2-9 are also the epilogue. Barriers per stage: full_a (this CTA's A bytes, fused form), full_b (leader:
+// B bytes of both CTAs, plus A bytes in the plain form), xformed (this CTA's 8 transform warps are done with the stage),
+// peer_ready (leader: the other CTA's relay thread has seen its xformed and fenced), empty (UMMAs have read the stage:
+// commit multicast to both CTAs). The writes of the transform reach the tensor core through one fence.proxy.async per
+// CTA and stage, executed by the thread that acquired the warps' barrier (the UMMA issuer in the leader, the relay
+// thread in the other CTA), not by the 256 writers. No TMA load is multicast. Every wait is bounded.
 #include <algorithm>
 #include <atomic>
+#include <cstdlib>
 #include <type_traits>
 
 #include "ce_grad_math.cuh"
@@ -36,6 +42,8 @@ namespace nm::ce {
 namespace {
 
 constexpr int kWideN = 512;                        // accumulator columns of a tile
+constexpr int kXWarps = 16;                        // transform warps (the first kEpiWarps of them are also the epilogue)
+constexpr int kWThreads = 64 + 32 * kXWarps;
 constexpr int kWStages = 4;
 constexpr int kWABytes = BM * BK * 2;              // 16 KiB: this CTA's 128 rows (or vocabulary entries) x 64 k
 constexpr int kWBHalfBytes = 128 * BK * 2;         // 16 KiB: this CTA's 128 of the 256 columns of one UMMA
@@ -47,7 +55,7 @@ constexpr int wide_smem_bytes(int epi) {
 }
 
 template <int EPI, bool A_MN, bool kXform>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kWThreads, 1)
 k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -62,8 +70,9 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   auto full_b = [&](int s) { return bar0 + 8u * (kWStages + s); };
   auto xformed = [&](int s) { return bar0 + 8u * (2 * kWStages + s); };
   auto empty_bar = [&](int s) { return bar0 + 8u * (3 * kWStages + s); };
-  const uint32_t tfull = bar0 + 8u * (4 * kWStages), tempty = bar0 + 8u * (4 * kWStages + 1);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kWStages + 2);
+  auto peer_ready = [&](int s) { return bar0 + 8u * (4 * kWStages + s); };
+  const uint32_t tfull = bar0 + 8u * (5 * kWStages), tempty = bar0 + 8u * (5 * kWStages + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5 * kWStages + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -73,8 +82,9 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int s = 0; s < kWStages; ++s) {
       mbar_init(full_a(s), 1);
       mbar_init(full_b(s), 1);
-      mbar_init(xformed(s), 2 * kEpiWarps);
+      mbar_init(xformed(s), kXWarps);
       mbar_init(empty_bar(s), 1);
+      mbar_init(peer_ready(s), 1);
     }
     mbar_init(tfull, 1);
     mbar_init(tempty, 2 * kEpiWarps);
@@ -117,6 +127,25 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (rank == 0) mbar_arrive_expect_tx(full_b(stage), 2 * (nh * kWBHalfBytes + (kXform ? 0 : kWABytes)));
           const uint32_t a_dst = sA + stage * kWABytes, b_dst = sB + stage * kWBBytes;
           const int k0 = kb * BK;
+          // ask L2 for the blocks a few stages beyond the ring, so that the loads that fill a stage find them there
+          if (p.prefetch > 0 && kb + p.prefetch < k_blocks) {
+            const int kp = k0 + p.prefetch * BK;
+            if (p.prefetch_what & 1) {
+              if constexpr (A_MN) {
+                if (p.a_3d) tma_prefetch_l2_3d(&tmA, 0, kp, m0 >> 6);
+                else { tma_prefetch_l2_2d(&tmA, m0, kp); tma_prefetch_l2_2d(&tmA, m0 + 64, kp); }
+              } else {
+                tma_prefetch_l2_2d(&tmA, kp, m0);
+              }
+            }
+            if (p.prefetch_what & 2) {
+              for (int u = 0; u < nh; ++u) {
+                const int n0 = ni * kWideN + u * BN + int(rank) * (BN / 2);
+                if (p.b_3d) tma_prefetch_l2_3d(&tmB, 0, kp, n0 >> 6);
+                else { tma_prefetch_l2_2d(&tmB, n0, kp); tma_prefetch_l2_2d(&tmB, n0 + 64, kp); }
+              }
+            }
+          }
           // A: in the fused form the bytes are counted on this CTA's own barrier (its transform warps wait there)
           if constexpr (A_MN) {
             if (p.a_3d) {
@@ -152,6 +181,22 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else if (warp == 1) {
+    if (kXform && lane == 0 && rank == 1) {
+      // ------------------------------------------------------------------ relay (the CTA that issues no UMMAs)
+      // Its transform warps arrive on a barrier of their own CTA (a CTA-scope release is cheap; a cluster-scope one
+      // from every warp was the longest stall of this kernel). This thread waits there, fences the writes towards the
+      // async proxy and tells the leader, stage by stage.
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = walker; tile < num_tiles && ok; tile += walkers) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(xformed(stage), phase, abort_flag, p.status, kErrTransformWait)) { ok = false; break; }
+          fence_proxy_async_smem();
+          mbar_arrive_cluster(mapa_shared(peer_ready(stage), 0));
+          if (++stage == kWStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
     if (lane == 0 && rank == 0) {
       // ------------------------------------------------------------------ UMMA issuer (leader CTA)
       constexpr uint32_t idesc = idesc_bf16_f32(2 * BM, BN, A_MN, true);
@@ -168,7 +213,12 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(full_b(stage), phase, abort_flag, p.status, kErrMmaWait)) { ok = false; break; }
           if constexpr (kXform) {
-            if (!mbar_wait_cluster(xformed(stage), phase, abort_flag, p.status, kErrMmaWait)) { ok = false; break; }
+            // this CTA's transform warps released their shared-memory writes on xformed; one proxy fence here, on the
+            // path from those writes to the UMMAs, orders them before the tensor core's reads. The other CTA's relay
+            // thread did the same for its half before it arrived on peer_ready.
+            if (!mbar_wait(xformed(stage), phase, abort_flag, p.status, kErrMmaWait)) { ok = false; break; }
+            fence_proxy_async_smem();
+            if (!mbar_wait_cluster(peer_ready(stage), phase, abort_flag, p.status, kErrMmaWait)) { ok = false; break; }
           }
           tc_fence_after();
           const uint32_t a_src = sA + stage * kWABytes, b_src = sB + stage * kWBBytes;
@@ -188,23 +238,26 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else {
-    // -------------------------------------------------------------------- transform + epilogue (warps 2-9)
-    const int w8 = warp - 2;
+    // -------------------------------------------------------------------- transform (warps 2-17) + epilogue (2-9)
+    const int w16 = warp - 2;
+    const bool drains = w16 < kEpiWarps;       // the first eight transform warps also drain the accumulator
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
-    const int colhalf = w8 >> 2;               // which 256 columns of the tile this warp drains
+    const int colhalf = (w16 >> 2) & 1;        // which 256 columns of the tile this warp drains
     const int r_local = quad * 32 + lane;
-    const uint32_t stg = sEpi + uint32_t(w8) * kEpiBufBytes;
+    const uint32_t stg = sEpi + uint32_t(w16 & (kEpiWarps - 1)) * kEpiBufBytes;
     float scale = 1.f;
     if constexpr (EPI == kEpiDx || EPI == kEpiDw) scale = p.scale ? __ldg(p.scale) : 1.f;
-    // transform geometry: 16 rows of the staged A block per warp, lane & 15 = row, lane >> 4 = which four of the eight
+    // transform geometry: 8 rows of the staged A block per warp, lane & 7 = row, lane >> 3 = which two of the eight
     // 16-byte pieces of that 128-byte row. Eight consecutive lanes touch eight different rows, so their swizzled
     // pieces fall into eight different bank groups.
-    const int xh = lane >> 4;
-    // K-major A (dX): 128 rows x 128 bytes, row = w8 * 16 + (lane & 15), fixed for the tile
-    // MN-major A (dW): two boxes of 64 k-rows x 128 bytes; box = w8 >> 2, k-row = (w8 & 3) * 16 + (lane & 15)
-    const int xrow = A_MN ? ((w8 & 3) * 16 + (lane & 15)) : (w8 * 16 + (lane & 15));
-    const uint32_t xoff = A_MN ? uint32_t((w8 >> 2) * kBoxBytesMN + xrow * 128) : uint32_t(xrow * 128);
+    const int xq = lane >> 3;
+    // K-major A (dX): 128 rows x 128 bytes, row = w16 * 8 + (lane & 7), fixed for the tile
+    // MN-major A (dW): two boxes of 64 k-rows x 128 bytes; box = w16 >> 3, k-row = (w16 & 7) * 8 + (lane & 7)
+    const int xrow = A_MN ? ((w16 & 7) * 8 + (lane & 7)) : (w16 * 8 + (lane & 7));
+    const uint32_t xoff = A_MN ? uint32_t((w16 >> 3) * kBoxBytesMN + xrow * 128) : uint32_t(xrow * 128);
+    const uint32_t piece0 = (uint32_t((xq * 2) ^ (xrow & 7)) << 4), piece1 = (uint32_t((xq * 2 + 1) ^ (xrow & 7)) << 4);
     const uint32_t lead_tempty = mapa_shared(tempty, 0);
+    const uint64_t ll = gradmath::pack_f32x2(gradmath::kLog2e, gradmath::kLog2e);
     int stage = 0; uint32_t phase = 0;
     int it = 0;
     bool alive = true;
@@ -227,42 +280,66 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int r = k0 + BK + xrow;
             if (kb + 1 < k_blocks && r < p.K) nxt = p.rowf[r];
           }
-          if (!mbar_wait<true>(full_a(stage), phase, abort_flag, p.status, kErrTransformWait)) { alive = false; break; }
+          const bool landed = p.xform_spin ? mbar_wait<false>(full_a(stage), phase, abort_flag, p.status, kErrTransformWait)
+                                           : mbar_wait<true>(full_a(stage), phase, abort_flag, p.status, kErrTransformWait);
+          if (!landed) { alive = false; break; }
           const uint32_t row_addr = sA + stage * kWABytes + xoff;
-          // first column of the store this thread's four pieces cover
-          const int vbase = A_MN ? (p.m_off + m0 + (w8 >> 2) * 64 + xh * 32) : (k0 + xh * 32);
-          const int tpos = rf.target - vbase;                       // 0 .. 31 when the target is among them
-          const int limit = A_MN ? 32 : (p.K - vbase);              // dX: columns at or beyond V are zero
-          uint4 v[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) v[i] = ld_shared_v4(row_addr + (uint32_t((xh * 4 + i) ^ (xrow & 7)) << 4));
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int hit = (tpos >> 3) == i ? (tpos & 7) : -1;
-            v[i] = gradmath::piece_bf16(v[i], rf.e, rf.a, rf.b, hit, limit - 8 * i);
+          // first column of the store this thread's two pieces cover
+          const int vbase = A_MN ? (p.m_off + m0 + (w16 >> 3) * 64 + xq * 16) : (k0 + xq * 16);
+          const int tpos = rf.target - vbase;                       // 0 .. 15 when the target is among them
+          const int limit = A_MN ? 16 : (p.K - vbase);              // dX: columns at or beyond V are zero
+          // the row's target, when it lies in these 16 columns (one thread, one K block per row): its raw logit is
+          // picked up before the pieces are rewritten and its value patched in afterwards
+          const bool has_target = static_cast<unsigned>(tpos) < 16u;
+          const uint32_t t_addr = row_addr + (tpos < 8 ? piece0 : piece1) + uint32_t(tpos & 7) * 2u;
+          uint16_t t_raw = 0;
+          if (has_target) t_raw = ld_shared_u16(t_addr);
+          if (p.xform_debug == 1) {            // timing experiment: the synchronisation alone (results are wrong)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(xformed(stage));
+            if constexpr (A_MN) rf = nxt;
+            if (++stage == kWStages) { stage = 0; phase ^= 1u; }
+            continue;
           }
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            st_shared_v4(row_addr + (uint32_t((xh * 4 + i) ^ (xrow & 7)) << 4), v[i].x, v[i].y, v[i].z, v[i].w);
-          fence_proxy_async_smem();
+          uint4 v0 = ld_shared_v4(row_addr + piece0), v1 = ld_shared_v4(row_addr + piece1);
+          if (p.xform_debug == 2) {            // timing experiment: loads and stores but no arithmetic
+          } else
+          if (limit >= 16) {                   // uniform over the CTA except in the last K block of a ragged vocabulary
+            const uint64_t ee = gradmath::pack_f32x2(rf.e, rf.e), aa = gradmath::pack_f32x2(rf.a, rf.a);
+            v0 = gradmath::piece_bf16_plain2(v0, ll, ee, aa);
+            v1 = gradmath::piece_bf16_plain2(v1, ll, ee, aa);
+          } else {
+            v0 = gradmath::piece_bf16(v0, rf.e, rf.a, 0.f, -1, limit);
+            v1 = gradmath::piece_bf16(v1, rf.e, rf.a, 0.f, -1, limit - 8);
+          }
+          st_shared_v4(row_addr + piece0, v0.x, v0.y, v0.z, v0.w);
+          st_shared_v4(row_addr + piece1, v1.x, v1.y, v1.z, v1.w);
+          if (has_target) st_shared_u16(t_addr, gradmath::target_element(t_raw, rf.e, rf.a, rf.b));
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(mapa_shared(xformed(stage), 0));
+          if (lane == 0) mbar_arrive(xformed(stage));   // CTA-scope release of the warp's writes
           if constexpr (A_MN) rf = nxt;
           if (++stage == kWStages) { stage = 0; phase ^= 1u; }
         }
         if (!alive) break;
       }
+      if (!drains) continue;
 
-      // ---- epilogue of the tile: 256 columns per warp in chunks of 32
+      // ---- epilogue of the tile: 256 columns per warp in chunks of 32 (the contraction is so long that nothing is
+      // gained by overlapping the accumulator loads with the stores)
       const int grow = m0 + r_local;
       const bool row_ok = grow < p.M;
       const bool warp_rows_ok = m0 + quad * 32 < p.M;
       if (!mbar_wait<true>(tfull, uint32_t(it) & 1u, abort_flag, p.status, kErrEpilogueWait)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(colhalf * BN);
-      auto process = [&](float* v, int c) {
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
         const int col0 = n0 + colhalf * BN + c * 32;
-        if (col0 >= p.N) return;               // uniform over the warp
+        if (col0 >= p.N) break;                // uniform over the warp
+        float v[32];
+        __syncwarp();
+        tmem_ld32(taddr + uint32_t(c * 32), v);
+        tmem_ld_wait(v);
         if constexpr (EPI == kEpiDx) {
           if (row_ok) epi_dx_chunk(p, v, grow, col0, scale);
         } else if constexpr (EPI == kEpiDw) {
@@ -285,30 +362,13 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               if (j < ncols) p.c[int64_t(grow) * p.ldc + col0 + j] = v[j];
           }
         }
-      };
-      constexpr int kChunks = BN / 32;
-      float va[32], vb[32];
-      __syncwarp();
-      tmem_ld32(taddr, va);
-#pragma unroll 1
-      for (int c = 0; c < kChunks; c += 2) {
-        tmem_ld_wait(va);
-        __syncwarp();
-        tmem_ld32(taddr + uint32_t((c + 1) * 32), vb);
-        process(va, c);
-        tmem_ld_wait(vb);
-        if (c + 2 < kChunks) {
-          __syncwarp();
-          tmem_ld32(taddr + uint32_t((c + 2) * 32), va);
-        }
-        process(vb, c + 1);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(lead_tempty);   // the leader's UMMA issuer may overwrite the accumulator
     }
     if constexpr (EPI == kEpiDw) {
-      if (lane == 0) bulk_wait<0>();           // every staged reduction has been performed
+      if (drains && lane == 0) bulk_wait<0>();  // every staged reduction has been performed
       __syncwarp();
     }
   }
@@ -336,11 +396,23 @@ void launch_wide(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap
   const int tiles = p.num_m * p.num_n;
   const int pairs = std::max(1, (sm_count() - std::max(0, sm_reserve)) / 2);
   const int grid = 2 * std::min(tiles, pairs);
-  kernel<<<dim3(unsigned(grid)), dim3(kThreads), kSmem, st>>>(ta, tb, tc, p);
+  kernel<<<dim3(unsigned(grid)), dim3(kWThreads), kSmem, st>>>(ta, tb, tc, p);
   NM_CUDA(cudaGetLastError());
 }
 
+int env_int(const char* name, int dflt) {
+  const char* e = std::getenv(name);
+  return e ? std::atoi(e) : dflt;
+}
+
 void fill_wide_tiles(GemmParams& p) {
+  static const int spin = env_int("NM_CE_XFORM_SPIN", 0), pre = env_int("NM_CE_PREFETCH", 0),
+                   what = env_int("NM_CE_PREFETCH_WHAT", 3);
+  static const int dbg = env_int("NM_CE_XFORM_DEBUG", 0);
+  p.xform_debug = dbg;
+  p.xform_spin = spin;
+  p.prefetch = pre;
+  p.prefetch_what = what;
   p.num_m = (p.M + 2 * BM - 1) / (2 * BM);
   p.num_n = (p.N + kWideN - 1) / kWideN;
   p.m_inner = 0;
