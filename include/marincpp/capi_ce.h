@@ -121,6 +121,22 @@ int nm_ce_forward_noalloc_status(void* stream, uint32_t* status_host);
 /* Test hook for the line above: points the short wait probe of nm_ce_test_wait_timeout at that status word. */
 int nm_ce_forward_noalloc_test_timeout(int64_t limit_cycles, void* stream);
 
+/* ---- sampled-softmax head (C++: include/marincpp/kernels/sampled_head.hpp). The reference names this head in its
+ *      output-head design (include/marincpp/model.hpp:236-239, docs/DESIGN.md:958) and ships no code for it. The
+ *      candidate set is the sorted unique set of the call's counted targets plus n_negatives ids
+ *      (neg_offset + j * nm_ce_sampled_stride(V)) mod V; W is gathered to W_P [p_max, D], the fused CE runs over the
+ *      candidate columns (unused ones masked out of the softmax), and dW_P is added into dw at the candidate rows.
+ *      p_max (a multiple of 8) must be at least min(V, T + n_negatives). x, w, dx bf16; dw [V, D] f32 (+=).
+ *      candidates_out [p_max] (sorted ids, -1 beyond the count) and n_candidates_out (device int) are optional. ------ */
+int64_t nm_ce_sampled_stride(int64_t V);
+uint64_t nm_ce_sampled_workspace_bytes(int64_t T, int D, int V, int p_max, int chunk_rows, int logits_store);
+int nm_ce_sampled_head(int rounding, int logits_store, const void* x, const void* w, const int32_t* targets,
+                       const float* weight, const float* grad_scale, float* loss_tok, float* lse, float* loss_partial,
+                       void* dx, int accumulate_dx, float* dw, int forward_only, int64_t T, int D, int V,
+                       int n_negatives, int64_t neg_offset, int p_max, int chunk_rows, int32_t* candidates_out,
+                       int32_t* n_candidates_out, void* workspace, void* stream, float z_loss_weight,
+                       int32_t ignore_index);
+
 /* ---- data-parallel dW reduction over NCCL (the role of the reference's include/marincpp/comm.hpp:22-58 GradReducer
  *      and of src/train/trainer.cpp:50,139): one communicator per process (one process per GPU) ------------------- */
 int nm_comm_unique_id(void* id128_host);                       /* rank 0: 128 bytes to broadcast to the other ranks */

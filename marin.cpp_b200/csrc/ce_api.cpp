@@ -179,7 +179,7 @@ struct CallKind {
 
 bool aligned(const void* p, uintptr_t to) { return reinterpret_cast<uintptr_t>(p) % to == 0; }
 
-CallKind require_call(CeImpl impl, const CeShape& s, const CeArgs& a, const void* ws) {
+CallKind require_call(CeImpl impl, const CeShape& s, const CeArgs& a, const void* ws, const RunOptions& opt) {
   CallKind k;
   NM_REQUIRE(a.x && a.w, "fused CE: x and w are required");
   NM_REQUIRE(a.targets && a.weight, "fused CE: targets and weight are required");
@@ -198,7 +198,8 @@ CallKind require_call(CeImpl impl, const CeShape& s, const CeArgs& a, const void
   }
   const bool inplace_accumulate = a.dx != nullptr && a.dx == a.x && a.accumulate_dx;
   NM_REQUIRE(!inplace_accumulate, "fused CE: dx may alias x or accumulate, not both");
-  NM_REQUIRE(a.logit_bias == nullptr || impl == CeImpl::A, "fused CE: only implementation A takes a logit_bias");
+  NM_REQUIRE(a.logit_bias == nullptr || impl == CeImpl::A || opt.allow_logit_bias,
+             "fused CE: only implementation A takes a logit_bias");
   if (k.reducer) {
     NM_REQUIRE(a.dw != nullptr && k.grads && !k.strict_dw,
                "fused CE: a dW reducer goes with a dw gradient and CeDwRound::None");
@@ -266,10 +267,10 @@ void run_forward(const Regions& w, const void* x, const void* wmat, const int32_
 }
 
 // ------------------------------------------------------------------------------------------------ one call
-void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, cudaStream_t st) {
+void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, cudaStream_t st, const RunOptions& opt) {
   require_shape(impl, s);
   if (s.T == 0) return;
-  const CallKind k = require_call(impl, s, a, ws);
+  const CallKind k = require_call(impl, s, a, ws, opt);
   const Regions w = layout_call(impl, s, ws);
   const int D = s.D, V = s.V;
   const int64_t io_row_bytes = int64_t(D) * int64_t(dtype_size(s.io));

@@ -19,20 +19,23 @@
 //     on. Per 64-deep K block a CTA evaluates 8192 exponentials against 1024 tensor cycles: half the SM's MUFU rate.
 //     Neither the separate pass nor a second copy of the gradient exists; the logits store is read-only here, so tiles
 //     that share A (the N tiles of a wide hidden size) simply transform it again.
-//   * Plain form: A is already n (the in-place pass ran); the warps 2-9 idle until the epilogue.
+//   * Plain form: A is already n (the in-place pass ran); the transform warps idle until the epilogue.
 //
-// Warp roles per CTA (576 threads): warp 0 TMA producer (one lane), warp 1 TMEM allocation + UMMA issue (one lane, leader
-// CTA only; in the other CTA that lane is the relay), warps 2-17 transform (four per scheduler: with two, the dependent
-// chain load - exponential - pack - store left the issue slots 70 % idle and the tensor pipe at 65 %), of which warps
-// 2-9 are also the epilogue. Barriers per stage: full_a (this CTA's A bytes, fused form), full_b (leader:
-// B bytes of both CTAs, plus A bytes in the plain form), xformed (this CTA's 8 transform warps are done with the stage),
-// peer_ready (leader: the other CTA's relay thread has seen its xformed and fenced), empty (UMMAs have read the stage:
-// commit multicast to both CTAs). The writes of the transform reach the tensor core through one fence.proxy.async per
-// CTA and stage, executed by the thread that acquired the warps' barrier (the UMMA issuer in the leader, the relay
-// thread in the other CTA), not by the 256 writers. No TMA load is multicast. Every wait is bounded.
+// Warp roles per CTA (704 threads): warp 0 TMA producer of B (one lane), warp 1 TMEM allocation + UMMA issue (one lane,
+// leader CTA only), warp 2 TMA producer of A (one lane), warps 3-18 transform (four per scheduler), of which warps
+// 3-10 are also the epilogue, warps 19-21 relays (one lane each, in the CTA that issues no UMMAs). A and B have rings of their own (6 and 4 or 3
+// stages): measured with the arithmetic of the transform switched off, the fused form was no faster, i.e. what it
+// costs is the longer way of an A block to the tensor core (load, wake the warps, their barrier, the relay, the
+// issuer), and a deeper A ring is what hides that.
+// Barriers: per A stage full_a (fused form: this CTA's A bytes; plain form: the leader's, for both CTAs), xformed (this
+// CTA's 16 transform warps are done with the stage), peer_ready (leader: the other CTA's relay thread has seen its
+// xformed and fenced), empty_a; per B stage full_b (leader: the B bytes of both CTAs), empty_b (the empties arrive in
+// both CTAs through the multicast commit once the UMMAs have read the stage). The writes of the transform reach the
+// tensor core through one fence.proxy.async per CTA and stage, executed by the thread that acquired the warps' barrier
+// (the UMMA issuer in the leader, the relay thread in the other CTA), not by the 512 writers. No TMA load is multicast.
+// Every wait is bounded.
 #include <algorithm>
 #include <atomic>
-#include <cstdlib>
 #include <type_traits>
 
 #include "ce_grad_math.cuh"
@@ -43,48 +46,65 @@ namespace {
 
 constexpr int kWideN = 512;                        // accumulator columns of a tile
 constexpr int kXWarps = 16;                        // transform warps (the first kEpiWarps of them are also the epilogue)
-constexpr int kWThreads = 64 + 32 * kXWarps;
-constexpr int kWStages = 4;
+constexpr int kFirstXWarp = 3;                     // warps 0, 1, 2: B producer, UMMA issuer / relay, A producer
+constexpr int kRelays = 3;                         // relay warps (after the transform warps); stage s belongs to relay s % 3
+constexpr int kWThreads = 32 * (kFirstXWarp + kXWarps + kRelays);
 constexpr int kWABytes = BM * BK * 2;              // 16 KiB: this CTA's 128 rows (or vocabulary entries) x 64 k
 constexpr int kWBHalfBytes = 128 * BK * 2;         // 16 KiB: this CTA's 128 of the 256 columns of one UMMA
 constexpr int kWBBytes = 2 * kWBHalfBytes;         // both 256-column halves of the tile
-constexpr int kWStageBytes = kWABytes + kWBBytes;  // 48 KiB
+// The two operands have rings of their own. A's way from HBM to the tensor core is the long one (HBM latency, then the
+// transform and two barrier hand-overs before the UMMAs may read it), so its ring is the deeper; B comes out of L2
+// and is consumed as it lands. dW gives one B stage to the staging tiles of its epilogue (its B operand, the x chunk,
+// stays in L2).
+__host__ __device__ constexpr int a_stages(int epi) { return 6; }
+__host__ __device__ constexpr int b_stages(int epi) { return epi == kEpiDw ? 3 : 4; }
 __host__ __device__ constexpr int wide_epi_bytes(int epi) { return epi == kEpiDw ? kEpiWarps * kEpiBufBytes : 0; }
+constexpr int kWBarrierBytes = 512;
 constexpr int wide_smem_bytes(int epi) {
-  return kWStages * kWStageBytes + wide_epi_bytes(epi) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  return a_stages(epi) * kWABytes + b_stages(epi) * kWBBytes + wide_epi_bytes(epi) + 1024 /*alignment slack*/ +
+         kWBarrierBytes;
 }
 
 template <int EPI, bool A_MN, bool kXform>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kWThreads, 1)
 k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  constexpr int kA = a_stages(EPI), kB = b_stages(EPI);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
-  const uint32_t sA = base, sB = base + kWStages * kWABytes;
-  const uint32_t sEpi = base + kWStages * kWStageBytes;
+  const uint32_t sA = base, sB = base + kA * kWABytes;
+  const uint32_t sEpi = sB + kB * kWBBytes;
   const uint32_t bar0 = sEpi + wide_epi_bytes(EPI);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kWStages * kWStageBytes + wide_epi_bytes(EPI));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kA * kWABytes + kB * kWBBytes + wide_epi_bytes(EPI));
+  // per A stage: full_a (fused: this CTA's bytes; plain: leader only, the bytes of both CTAs), xformed (this CTA's
+  // transform warps are done), peer_ready (leader: the other CTA's relay has seen its xformed), empty_a
   auto full_a = [&](int s) { return bar0 + 8u * s; };
-  auto full_b = [&](int s) { return bar0 + 8u * (kWStages + s); };
-  auto xformed = [&](int s) { return bar0 + 8u * (2 * kWStages + s); };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (3 * kWStages + s); };
-  auto peer_ready = [&](int s) { return bar0 + 8u * (4 * kWStages + s); };
-  const uint32_t tfull = bar0 + 8u * (5 * kWStages), tempty = bar0 + 8u * (5 * kWStages + 1);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5 * kWStages + 2);
+  auto xformed = [&](int s) { return bar0 + 8u * (kA + s); };
+  auto peer_ready = [&](int s) { return bar0 + 8u * (2 * kA + s); };
+  auto empty_a = [&](int s) { return bar0 + 8u * (3 * kA + s); };
+  // per B stage: full_b (leader: the bytes of both CTAs), empty_b
+  auto full_b = [&](int s) { return bar0 + 8u * (4 * kA + s); };
+  auto empty_b = [&](int s) { return bar0 + 8u * (4 * kA + kB + s); };
+  const uint32_t tfull = bar0 + 8u * (4 * kA + 2 * kB), tempty = tfull + 8u;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kA + 2 * kB + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  static_assert((4 * kA + 2 * kB + 2) * 8 + 8 <= kWBarrierBytes, "barrier region too small");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();          // 0 = leader
   const int walker = int(blockIdx.x >> 1), walkers = int(gridDim.x >> 1);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kWStages; ++s) {
+    for (int s = 0; s < kA; ++s) {
       mbar_init(full_a(s), 1);
-      mbar_init(full_b(s), 1);
       mbar_init(xformed(s), kXWarps);
-      mbar_init(empty_bar(s), 1);
       mbar_init(peer_ready(s), 1);
+      mbar_init(empty_a(s), 1);
+    }
+    for (int s = 0; s < kB; ++s) {
+      mbar_init(full_b(s), 1);
+      mbar_init(empty_b(s), 1);
     }
     mbar_init(tfull, 1);
     mbar_init(tempty, 2 * kEpiWarps);
@@ -111,98 +131,89 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp == 0) {
     if (lane == 0) {
-      // ------------------------------------------------------------------ TMA producer (both CTAs)
+      // ------------------------------------------------------------------ B producer (both CTAs)
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       const uint64_t pol_last = l2_policy_evict_last();   // dW re-reads the whole x chunk for every vocabulary tile
       for (int tile = walker; tile < num_tiles && ok; tile += walkers) {
         int mi, ni;
         decode(tile, mi, ni);
-        const int m0 = p.m_off + mi * (2 * BM) + int(rank) * BM;
         const int nh = halves(ni);
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait<true>(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kErrProducerWait)) { ok = false; break; }
-          const uint32_t lead_b = mapa_shared(full_b(stage), 0);
-          if constexpr (kXform) mbar_arrive_expect_tx(full_a(stage), kWABytes);
-          if (rank == 0) mbar_arrive_expect_tx(full_b(stage), 2 * (nh * kWBHalfBytes + (kXform ? 0 : kWABytes)));
-          const uint32_t a_dst = sA + stage * kWABytes, b_dst = sB + stage * kWBBytes;
+          if (!mbar_wait<true>(empty_b(stage), phase ^ 1u, abort_flag, p.status, kErrProducerWait)) { ok = false; break; }
+          const uint32_t lead = mapa_shared(full_b(stage), 0);
+          if (rank == 0) mbar_arrive_expect_tx(full_b(stage), 2 * nh * kWBHalfBytes);
           const int k0 = kb * BK;
-          // ask L2 for the blocks a few stages beyond the ring, so that the loads that fill a stage find them there
-          if (p.prefetch > 0 && kb + p.prefetch < k_blocks) {
-            const int kp = k0 + p.prefetch * BK;
-            if (p.prefetch_what & 1) {
-              if constexpr (A_MN) {
-                if (p.a_3d) tma_prefetch_l2_3d(&tmA, 0, kp, m0 >> 6);
-                else { tma_prefetch_l2_2d(&tmA, m0, kp); tma_prefetch_l2_2d(&tmA, m0 + 64, kp); }
-              } else {
-                tma_prefetch_l2_2d(&tmA, kp, m0);
-              }
-            }
-            if (p.prefetch_what & 2) {
-              for (int u = 0; u < nh; ++u) {
-                const int n0 = ni * kWideN + u * BN + int(rank) * (BN / 2);
-                if (p.b_3d) tma_prefetch_l2_3d(&tmB, 0, kp, n0 >> 6);
-                else { tma_prefetch_l2_2d(&tmB, n0, kp); tma_prefetch_l2_2d(&tmB, n0 + 64, kp); }
-              }
-            }
-          }
-          // A: in the fused form the bytes are counted on this CTA's own barrier (its transform warps wait there)
-          if constexpr (A_MN) {
-            if (p.a_3d) {
-              if constexpr (kXform) tma_load_3d(a_dst, &tmA, full_a(stage), 0, k0, m0 >> 6);
-              else tma_pair_load_3d(a_dst, &tmA, lead_b, 0, k0, m0 >> 6);
-            } else {
-#pragma unroll
-              for (int j = 0; j < BM / 64; ++j) {
-                if constexpr (kXform) tma_load_2d(a_dst + j * kBoxBytesMN, &tmA, full_a(stage), m0 + j * 64, k0);
-                else tma_pair_load_2d(a_dst + j * kBoxBytesMN, &tmA, lead_b, m0 + j * 64, k0);
-              }
-            }
-          } else {
-            if constexpr (kXform) tma_load_2d(a_dst, &tmA, full_a(stage), k0, m0);
-            else tma_pair_load_2d(a_dst, &tmA, lead_b, k0, m0);
-          }
           for (int u = 0; u < nh; ++u) {
             const int n0 = ni * kWideN + u * BN + int(rank) * (BN / 2);
-            const uint32_t dst = b_dst + u * kWBHalfBytes;
+            const uint32_t dst = sB + stage * kWBBytes + u * kWBHalfBytes;
             if (p.b_3d) {
-              if constexpr (EPI == kEpiDw) tma_pair_load_3d_hint(dst, &tmB, lead_b, 0, k0, n0 >> 6, pol_last);
-              else tma_pair_load_3d(dst, &tmB, lead_b, 0, k0, n0 >> 6);
+              if constexpr (EPI == kEpiDw) tma_pair_load_3d_hint(dst, &tmB, lead, 0, k0, n0 >> 6, pol_last);
+              else tma_pair_load_3d(dst, &tmB, lead, 0, k0, n0 >> 6);
             } else {
 #pragma unroll
               for (int j = 0; j < 2; ++j) {
-                if constexpr (EPI == kEpiDw) tma_pair_load_2d_hint(dst + j * kBoxBytesMN, &tmB, lead_b, n0 + j * 64, k0, pol_last);
-                else tma_pair_load_2d(dst + j * kBoxBytesMN, &tmB, lead_b, n0 + j * 64, k0);
+                if constexpr (EPI == kEpiDw) tma_pair_load_2d_hint(dst + j * kBoxBytesMN, &tmB, lead, n0 + j * 64, k0, pol_last);
+                else tma_pair_load_2d(dst + j * kBoxBytesMN, &tmB, lead, n0 + j * 64, k0);
               }
             }
           }
-          if (++stage == kWStages) { stage = 0; phase ^= 1u; }
+          if (++stage == kB) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ A producer (both CTAs)
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = walker; tile < num_tiles && ok; tile += walkers) {
+        int mi, ni;
+        decode(tile, mi, ni);
+        const int m0 = p.m_off + mi * (2 * BM) + int(rank) * BM;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait<true>(empty_a(stage), phase ^ 1u, abort_flag, p.status, kErrProducerWait)) { ok = false; break; }
+          const uint32_t a_dst = sA + stage * kWABytes;
+          const int k0 = kb * BK;
+          if constexpr (kXform) {
+            // the bytes are counted on this CTA's own barrier: its transform warps wait there
+            mbar_arrive_expect_tx(full_a(stage), kWABytes);
+            if constexpr (A_MN) {
+              if (p.a_3d) {
+                tma_load_3d(a_dst, &tmA, full_a(stage), 0, k0, m0 >> 6);
+              } else {
+#pragma unroll
+                for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * kBoxBytesMN, &tmA, full_a(stage), m0 + j * 64, k0);
+              }
+            } else {
+              tma_load_2d(a_dst, &tmA, full_a(stage), k0, m0);
+            }
+          } else {
+            // the bytes of both CTAs are counted on the leader's barrier, which only the leader arms
+            const uint32_t lead = mapa_shared(full_a(stage), 0);
+            if (rank == 0) mbar_arrive_expect_tx(full_a(stage), 2 * kWABytes);
+            if constexpr (A_MN) {
+              if (p.a_3d) {
+                tma_pair_load_3d(a_dst, &tmA, lead, 0, k0, m0 >> 6);
+              } else {
+#pragma unroll
+                for (int j = 0; j < BM / 64; ++j) tma_pair_load_2d(a_dst + j * kBoxBytesMN, &tmA, lead, m0 + j * 64, k0);
+              }
+            } else {
+              tma_pair_load_2d(a_dst, &tmA, lead, k0, m0);
+            }
+          }
+          if (++stage == kA) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
-    if (kXform && lane == 0 && rank == 1) {
-      // ------------------------------------------------------------------ relay (the CTA that issues no UMMAs)
-      // Its transform warps arrive on a barrier of their own CTA (a CTA-scope release is cheap; a cluster-scope one
-      // from every warp was the longest stall of this kernel). This thread waits there, fences the writes towards the
-      // async proxy and tells the leader, stage by stage.
-      int stage = 0; uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = walker; tile < num_tiles && ok; tile += walkers) {
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(xformed(stage), phase, abort_flag, p.status, kErrTransformWait)) { ok = false; break; }
-          fence_proxy_async_smem();
-          mbar_arrive_cluster(mapa_shared(peer_ready(stage), 0));
-          if (++stage == kWStages) { stage = 0; phase ^= 1u; }
-        }
-      }
-    }
     if (lane == 0 && rank == 0) {
       // ------------------------------------------------------------------ UMMA issuer (leader CTA)
       constexpr uint32_t idesc = idesc_bf16_f32(2 * BM, BN, A_MN, true);
-      int stage = 0; uint32_t phase = 0;
+      int sa = 0, sb = 0; uint32_t pa = 0, pb = 0;
       int it = 0;
-      bool ok = true;
+      bool ok = true, ahead = false;
       for (int tile = walker; tile < num_tiles && ok; tile += walkers, ++it) {
         int mi, ni;
         decode(tile, mi, ni);
@@ -211,17 +222,35 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!mbar_wait_cluster(tempty, (uint32_t(it) & 1u) ^ 1u, abort_flag, p.status, kErrTmemFreeWait)) break;
         tc_fence_after();
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(full_b(stage), phase, abort_flag, p.status, kErrMmaWait)) { ok = false; break; }
-          if constexpr (kXform) {
-            // this CTA's transform warps released their shared-memory writes on xformed; one proxy fence here, on the
-            // path from those writes to the UMMAs, orders them before the tensor core's reads. The other CTA's relay
-            // thread did the same for its half before it arrived on peer_ready.
-            if (!mbar_wait(xformed(stage), phase, abort_flag, p.status, kErrMmaWait)) { ok = false; break; }
-            fence_proxy_async_smem();
-            if (!mbar_wait_cluster(peer_ready(stage), phase, abort_flag, p.status, kErrMmaWait)) { ok = false; break; }
+          // `ahead`: all barriers of this K block were seen complete by the look-ahead of the previous iteration
+          if (!ahead) {
+            if constexpr (kXform) {
+              if (!mbar_wait(xformed(sa), pa, abort_flag, p.status, kErrMmaWait)) { ok = false; break; }
+              if (!mbar_wait_cluster(peer_ready(sa), pa, abort_flag, p.status, kErrMmaWait)) { ok = false; break; }
+            } else {
+              if (!mbar_wait(full_a(sa), pa, abort_flag, p.status, kErrMmaWait)) { ok = false; break; }
+            }
+            if (!mbar_wait(full_b(sb), pb, abort_flag, p.status, kErrMmaWait)) { ok = false; break; }
           }
+          // this CTA's transform warps released their shared-memory writes on xformed; one proxy fence here, on the
+          // path from those writes to the UMMAs, orders them before the tensor core's reads. The other CTA's relay
+          // thread did the same for its half before it arrived on peer_ready.
+          if constexpr (kXform) fence_proxy_async_smem();
           tc_fence_after();
-          const uint32_t a_src = sA + stage * kWABytes, b_src = sB + stage * kWBBytes;
+          // Look ahead: test the next K block's barriers now, without blocking. A test is a shared-memory round trip
+          // of about a hundred cycles (measured with clock64 in this thread: 90 - 110 each), and three of them in a row
+          // between two K blocks let the queue of issued UMMAs (about a third of a K block deep) run dry. Issued here,
+          // they return while the UMMAs below wait for queue slots.
+          const int na = sa + 1 == kA ? 0 : sa + 1, nb = sb + 1 == kB ? 0 : sb + 1;
+          const uint32_t npa = sa + 1 == kA ? pa ^ 1u : pa, npb = sb + 1 == kB ? pb ^ 1u : pb;
+          bool next_ready = false;
+          if (kb + 1 < k_blocks) {
+            bool ra;
+            if constexpr (kXform) ra = mbar_try_wait(xformed(na), npa) & mbar_try_wait_cluster(peer_ready(na), npa);
+            else ra = mbar_try_wait(full_a(na), npa);
+            next_ready = ra & mbar_try_wait(full_b(nb), npb);
+          }
+          const uint32_t a_src = sA + sa * kWABytes, b_src = sB + sb * kWBBytes;
           for (int u = 0; u < nh; ++u) {
 #pragma unroll
             for (int k = 0; k < BK / UK; ++k) {
@@ -231,15 +260,41 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               umma_pair_bf16(tmem_base + uint32_t(u * BN), ad, bd, idesc, (kb | k) != 0);
             }
           }
-          umma_pair_commit(empty_bar(stage), 3);
-          if (++stage == kWStages) { stage = 0; phase ^= 1u; }
+          // both stages are free again, in both CTAs, once these UMMAs have read them
+          umma_pair_commit(empty_a(sa), 3);
+          umma_pair_commit(empty_b(sb), 3);
+          sa = na; pa = npa; sb = nb; pb = npb;
+          ahead = next_ready;
         }
+        ahead = false;
         if (ok) umma_pair_commit(tfull, 3);
       }
     }
+  } else if (warp >= kFirstXWarp + kXWarps) {
+    if (kXform && lane == 0 && rank == 1) {
+      // ------------------------------------------------------------------ relays (the CTA that issues no UMMAs)
+      // Its transform warps arrive on a barrier of their own CTA (a CTA-scope release is cheap). A relay thread waits
+      // there, fences the writes towards the async proxy and tells the leader with a cluster-scope release, which
+      // takes the issuing thread longer than a K block lasts: hence three relay threads in three warps, each
+      // serving every third stage, so that their arrivals overlap.
+      static_assert(a_stages(EPI) % kRelays == 0, "every stage must always meet the same relay");
+      const int me = warp - (kFirstXWarp + kXWarps);
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = walker; tile < num_tiles && ok; tile += walkers) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (stage % kRelays == me) {
+            if (!mbar_wait(xformed(stage), phase, abort_flag, p.status, kErrTransformWait)) { ok = false; break; }
+            fence_proxy_async_smem();
+            mbar_arrive_cluster(mapa_shared(peer_ready(stage), 0));
+          }
+          if (++stage == kA) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
   } else {
-    // -------------------------------------------------------------------- transform (warps 2-17) + epilogue (2-9)
-    const int w16 = warp - 2;
+    // -------------------------------------------------------------------- transform (16 warps) + epilogue (first 8)
+    const int w16 = warp - kFirstXWarp;
     const bool drains = w16 < kEpiWarps;       // the first eight transform warps also drain the accumulator
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
     const int colhalf = (w16 >> 2) & 1;        // which 256 columns of the tile this warp drains
@@ -280,9 +335,7 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int r = k0 + BK + xrow;
             if (kb + 1 < k_blocks && r < p.K) nxt = p.rowf[r];
           }
-          const bool landed = p.xform_spin ? mbar_wait<false>(full_a(stage), phase, abort_flag, p.status, kErrTransformWait)
-                                           : mbar_wait<true>(full_a(stage), phase, abort_flag, p.status, kErrTransformWait);
-          if (!landed) { alive = false; break; }
+          if (!mbar_wait<true>(full_a(stage), phase, abort_flag, p.status, kErrTransformWait)) { alive = false; break; }
           const uint32_t row_addr = sA + stage * kWABytes + xoff;
           // first column of the store this thread's two pieces cover
           const int vbase = A_MN ? (p.m_off + m0 + (w16 >> 3) * 64 + xq * 16) : (k0 + xq * 16);
@@ -294,16 +347,7 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t t_addr = row_addr + (tpos < 8 ? piece0 : piece1) + uint32_t(tpos & 7) * 2u;
           uint16_t t_raw = 0;
           if (has_target) t_raw = ld_shared_u16(t_addr);
-          if (p.xform_debug == 1) {            // timing experiment: the synchronisation alone (results are wrong)
-            __syncwarp();
-            if (lane == 0) mbar_arrive(xformed(stage));
-            if constexpr (A_MN) rf = nxt;
-            if (++stage == kWStages) { stage = 0; phase ^= 1u; }
-            continue;
-          }
           uint4 v0 = ld_shared_v4(row_addr + piece0), v1 = ld_shared_v4(row_addr + piece1);
-          if (p.xform_debug == 2) {            // timing experiment: loads and stores but no arithmetic
-          } else
           if (limit >= 16) {                   // uniform over the CTA except in the last K block of a ragged vocabulary
             const uint64_t ee = gradmath::pack_f32x2(rf.e, rf.e), aa = gradmath::pack_f32x2(rf.a, rf.a);
             v0 = gradmath::piece_bf16_plain2(v0, ll, ee, aa);
@@ -318,7 +362,7 @@ k_ce_grad_wide(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           __syncwarp();
           if (lane == 0) mbar_arrive(xformed(stage));   // CTA-scope release of the warp's writes
           if constexpr (A_MN) rf = nxt;
-          if (++stage == kWStages) { stage = 0; phase ^= 1u; }
+          if (++stage == kA) { stage = 0; phase ^= 1u; }
         }
         if (!alive) break;
       }
@@ -400,19 +444,7 @@ void launch_wide(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap
   NM_CUDA(cudaGetLastError());
 }
 
-int env_int(const char* name, int dflt) {
-  const char* e = std::getenv(name);
-  return e ? std::atoi(e) : dflt;
-}
-
 void fill_wide_tiles(GemmParams& p) {
-  static const int spin = env_int("NM_CE_XFORM_SPIN", 0), pre = env_int("NM_CE_PREFETCH", 0),
-                   what = env_int("NM_CE_PREFETCH_WHAT", 3);
-  static const int dbg = env_int("NM_CE_XFORM_DEBUG", 0);
-  p.xform_debug = dbg;
-  p.xform_spin = spin;
-  p.prefetch = pre;
-  p.prefetch_what = what;
   p.num_m = (p.M + 2 * BM - 1) / (2 * BM);
   p.num_n = (p.N + kWideN - 1) / kWideN;
   p.m_inner = 0;

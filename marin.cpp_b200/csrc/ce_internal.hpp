@@ -95,8 +95,12 @@ struct ProfScope {                                           // records begin / 
   int slot_; cudaStream_t st_;
 };
 
-// One call (the C++ API and the C ABI both end here).
-void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, cudaStream_t st);
+// One call (the C++ API and the C ABI both end here). Options that only callers inside the library may set:
+struct RunOptions {
+  bool allow_logit_bias = false;   // a logit bias with bf16 io and any implementation value (the sampled head's mask)
+};
+void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, cudaStream_t st,
+         const RunOptions& opt = RunOptions{});
 void readout(CeImpl impl, Rounding r, const CeShape& s, const ReadoutCall& c, const CeArgs& base, float eps, void* ws,
              cudaStream_t st);
 // Forward only on caller-provided forward regions (layout_forward): what run() does for a call without gradients.

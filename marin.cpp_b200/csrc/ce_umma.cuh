@@ -48,7 +48,6 @@ struct GemmParams {
   float* c; int64_t ldc;
   // gradient kernels that form n on the fly: per-row factors, indexed by the row of the logits store
   const RowFactors* rowf;
-  int xform_spin, prefetch, prefetch_what, xform_debug;
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {

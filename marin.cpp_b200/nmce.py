@@ -39,6 +39,10 @@ SIGS = {
     "nm_ce_suggest_chunk_rows": (I32, [I64]),
     "nm_ce_test_gemm": (I32, [I32, VP, I64, VP, I64, VP, I64, I32, I32, I32, VP, VP, VP]),
     "nm_ce_set_grad_path": (I32, [I32]),
+    "nm_ce_sampled_stride": (I64, [I64]),
+    "nm_ce_sampled_workspace_bytes": (U64, [I64, I32, I32, I32, I32, I32]),
+    "nm_ce_sampled_head": (I32, [I32, I32, VP, VP, VP, VP, VP, VP, VP, VP, VP, I32, VP, I32, I64, I32, I32, I32, I64, I32,
+                                 I32, VP, VP, VP, VP, F32, C.c_int32]),
     "nm_ce_forward_noalloc_status": (I32, [VP, VP]),
     "nm_ce_forward_noalloc_test_timeout": (I32, [I64, VP]),
     "nm_rmsnorm_fwd": (I32, [I32, I32, VP, VP, VP, VP, I64, I32, F32, VP]),
@@ -75,7 +79,7 @@ SIGS = {
     "nm_head_adamh_scalars": (I32, [VP, VP, VP]),
 }
 NO_STATUS = {"nm_version", "nm_last_error", "nm_device_arch", "nm_ce_workspace_bytes", "nm_ce_set_backends",
-             "nm_ce_device_arch", "nm_ce_set_fast_stats_exp", "nm_norm_partial_rows", "nm_head_adamh_owned_elems", "nm_ce_suggest_chunk_rows"}
+             "nm_ce_device_arch", "nm_ce_set_fast_stats_exp", "nm_ce_sampled_stride", "nm_ce_sampled_workspace_bytes", "nm_norm_partial_rows", "nm_head_adamh_owned_elems", "nm_ce_suggest_chunk_rows"}
 
 IMPLS = {"A": 0, "B1": 1, "B1.5": 2, "B2": 3}
 LEV, ACC = 0, 1
