@@ -85,7 +85,7 @@ int nm_ce_set_cta_pair(int logits, int dgrad, int wgrad);
  * 0 = an in-place pass over the logits store writes n, dX / dW run on 128 x 256 tiles; 1 = the same pass, dX / dW on
  * CTA pairs with 256 x 512 tiles (one 512-column TMEM accumulator); 2 = no pass: dX / dW read the raw logits and form
  * n in shared memory ahead of the tensor-core instructions (256 x 512 tiles); -1 = chosen per call (the default: 2 for
- * hidden sizes up to 512, else 0). Loss, lse and dX are bit-identical across the three; dW differs only by summation
+ * hidden sizes up to 1024, else 0). Loss, lse and dX are bit-identical across the three; dW differs only by summation
  * order between tile forms. Calls with an f32 logits store or f32 io always take form 0. Process-wide. No counterpart
  * in the reference (its nm_ce_set_backends chooses between its own kernels and cuBLASLt). */
 int nm_ce_set_grad_path(int path);

@@ -72,16 +72,18 @@ void set_grad_path(int path) {
   g_grad_path.store(path, std::memory_order_relaxed);
 }
 
-// Which form pays was measured per hidden size on a B200 with the forms alternated inside one process. Forming n
-// inside the contractions removes the in-place pass (4 bytes per logit at the HBM rate, a fifth of the step at hidden
-// 512) at the price of one exponential per staged logit per tile that reads it: a clear gain while one 512-column tile
-// covers the hidden size.
+// Which form pays was measured per hidden size on a B200, all three forms in turn on the same box (131072 rows, vocabulary
+// 128256; ms per step fused / pass + wide tiles / pass + 128 x 256 tiles): hidden 512: 48.6 / 55.5 / 56.3; 1024: 90.5 /
+// 93.3 / 95.6; 2048: 177.2 / 177.8 / 174.4. Forming n inside the contractions removes the in-place pass (4 bytes per
+// logit at the HBM rate: a fifth of the step at hidden 512) but every 512-column tile that reads a block of logits
+// transforms it again, and the transform's shared-memory traffic slows the UMMAs it runs beside; at hidden 2048 (four
+// tiles per block, a step that is bound by board power) that costs what the pass saved.
 GradPath grad_path_for(int D, int rows, bool plain_bf16) {
   (void)rows;
   if (!plain_bf16) return kPassClassic;
   const int forced = g_grad_path.load(std::memory_order_relaxed);
   if (forced != kPathAuto) return GradPath(forced);
-  return D <= 512 ? kFusedWide : kPassClassic;
+  return D <= 1024 ? kFusedWide : kPassClassic;
 }
 
 // ------------------------------------------------------------------------------------------------ profiling
