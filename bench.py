@@ -336,8 +336,8 @@ def measure(args, cfg, name, env, steps, warmup, with_e2e):
     def ce(x_in, y_in, wt_in, r, last):
         lib.nm_fused_linear_ce_ex(1, 0, 1, 1, nmce.ptr(x_in), nmce.ptr(W), nmce.ptr(y_in), nmce.ptr(wt_in),
                                   nmce.ptr(gs), None, nmce.ptr(loss), nmce.ptr(lse), nmce.ptr(lp[r]), nmce.ptr(dx), 0,
-                                  nmce.ptr(dw), None, 0, 0, T, D, V, chunk, nmce.ptr(ws), sp, float(L), -100,
-                                  reducer if last else None)
+                                  nmce.ptr(dw), None, 0, int(args.forward_only), T, D, V, chunk, nmce.ptr(ws), sp, float(L),
+                                  -100, reducer if (last and not args.forward_only) else None)
 
     if R > 1:   # pls: every layer's readout state goes through the readout entry point (norm + CE + norm backward)
         gain = torch.ones(D, dtype=torch.bfloat16, device=dev)
@@ -604,9 +604,14 @@ def main():
     ap.add_argument("--grad-path", type=int, default=-1,
                     help="how dX / dW get the normalised gradient: 0 in-place pass + 128x256 tiles, 1 pass + 256x512 pair "
                          "tiles, 2 formed inside the pair-tile kernels (no pass); -1: chosen per call")
+    ap.add_argument("--tail-order", type=int, default=1,
+                    help="last chunk with a dW reducer: 1 dX first on all SMs, then dW buckets beside the reductions; 0 dW "
+                         "buckets first and dX beside the reductions")
     ap.add_argument("--zero1", action="store_true",
                     help="reduce dW to its owners (reduce-scatter), AdamH on owned elements and all-gather of the bf16 "
                          "head inside every step, instead of the dW all-reduce (the optimizer then is in the timing)")
+    ap.add_argument("--forward-only", action="store_true",
+                    help="statistics and loss only (the evaluation path; also the small case of the logits kernel without its store)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg")
     ap.add_argument("--no-others", action="store_true",
@@ -638,6 +643,7 @@ def main():
     if args.cta_pair:
         lib.nm_ce_set_cta_pair(*[int(ch) for ch in args.cta_pair])
     lib.nm_ce_set_grad_path(args.grad_path)
+    lib.nm_ce_set_tail_order(args.tail_order)
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -704,7 +710,7 @@ def main():
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD[args.config] + (f" [tokens overridden to {T}]" if args.tokens > 0 else ""),
                    "tokens_per_gpu": R * T, "hidden": D, "vocab": V,
-                   "chunk_rows": chunk, "readouts": R, "grad_path": args.grad_path,
+                   "chunk_rows": chunk, "readouts": R, "grad_path": args.grad_path, "tail_order": args.tail_order, "forward_only": args.forward_only,
                    "parallelism": f"dp{world} (rows sharded, W replicated)",
                    "dw_allreduce": ((f"f32 reduce-scatter to owners, {args.buckets} buckets, overlapped with the last dX"
                                      if args.zero1 else

@@ -237,6 +237,10 @@ int nm_ce_set_cta_pair(int logits, int dgrad, int wgrad) {
   return guarded([&] { nm::ce::set_cta_pair(logits, dgrad, wgrad); });
 }
 
+int nm_ce_set_tail_order(int order) {
+  return guarded([&] { nm::ce::set_tail_order(order); });
+}
+
 int nm_ce_set_grad_path(int path) {
   return guarded([&] { nm::ce::set_grad_path(path); });
 }

@@ -55,6 +55,7 @@ namespace {
 std::atomic<int> g_backends{3 << 2};        // dgrad | wgrad << 1 | sm90 << 2, as nm_ce_set_backends packs it
 std::atomic<int> g_fast_stats_exp{0};
 std::atomic<int> g_grad_path{kPathAuto};
+std::atomic<int> g_tail_order{1};
 }  // namespace
 
 int exchange_backends(int dgrad_own, int wgrad_own, int sm90) {
@@ -66,6 +67,12 @@ int exchange_backends(int dgrad_own, int wgrad_own, int sm90) {
   return old;
 }
 int exchange_fast_stats_exp(int on) { return g_fast_stats_exp.exchange(on ? 1 : 0, std::memory_order_relaxed); }
+
+int tail_order() { return g_tail_order.load(std::memory_order_relaxed); }
+void set_tail_order(int order) {
+  NM_REQUIRE(order == 0 || order == 1, "tail order: 0 (dW buckets, then dX beside the reductions) or 1 (dX first)");
+  g_tail_order.store(order, std::memory_order_relaxed);
+}
 
 void set_grad_path(int path) {
   NM_REQUIRE(path >= kPathAuto && path <= kFusedWide, "gradient path: -1 (per call), 0, 1 or 2");
@@ -314,8 +321,9 @@ void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, c
     }
     const int64_t ldn = k.store_f32 ? 2 * w.ldS : w.ldS;   // bf16 elements between rows of n
 
-    // dW before dX: every kernel that reads x has been issued before dX (which may be x) is written
-    if (dw_into) {
+    const bool bucketed = k.reducer != nullptr && last_chunk;
+    auto issue_dw = [&] {
+      if (!dw_into) return;
       int reserve = 0;   // SMs left to the collective once a bucket reduction may be in flight
       auto wgrad_range = [&](int v0, int v1) {
         ProfScope t(3, st);
@@ -332,7 +340,7 @@ void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, c
           launch_wgrad(g, st);
         }
       };
-      if (k.reducer && last_chunk) {
+      if (bucketed) {
         // the last chunk completes dW range by range, and each range's reduction starts while the next is computed
         for (int b = 0; b < k.reducer->n_buckets(); ++b) {
           int v0 = 0, v1 = 0;
@@ -344,8 +352,9 @@ void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, c
       } else {
         wgrad_range(0, V);
       }
-    }
-    if (a.dx) {
+    };
+    auto issue_dx = [&](bool beside_reductions) {
+      if (!a.dx) return;
       void* dx_c = rows_from(a.dx, r0, io_row_bytes);
       ProfScope t(4, st);
       if (k.f32io) {   // W = hi + lo (hi at column 0, lo at column D of the split copy), f32 output accumulated
@@ -358,11 +367,23 @@ void run(CeImpl impl, Rounding r, const CeShape& s, const CeArgs& a, void* ws, c
       } else {
         DgradArgs g{w.store, ldn, a.w, int64_t(D), n, D, V, a.grad_scale, a.accumulate_dx ? dx_c : nullptr, dx_c,
                     r == Rounding::Levanter ? 1 : 2, false, w.status};
-        if (k.reducer && last_chunk) g.sm_reserve = comm_sms();   // the bucket reductions run beside this kernel
+        if (beside_reductions) g.sm_reserve = comm_sms();
         g.wide = wide;
         g.rowf = on_the_fly;
         launch_dgrad(g, st);
       }
+    };
+    // The order of a chunk is dW, then dX: every kernel that reads x has been issued before dX (which may be x) is
+    // written. One exception: the last chunk of a call whose dW is reduced bucket by bucket, when dX does not land on
+    // x. There dX goes first, on every SM, and only the dW buckets share the GPU with the reductions of their
+    // predecessors; what stays exposed is the reduction of the last bucket alone.
+    const bool dx_first = bucketed && a.dx != nullptr && a.dx != a.x && tail_order() == 1;
+    if (dx_first) {
+      issue_dx(false);
+      issue_dw();
+    } else {
+      issue_dw();
+      issue_dx(bucketed);
     }
   }
 }

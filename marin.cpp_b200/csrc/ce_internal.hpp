@@ -82,6 +82,10 @@ int exchange_fast_stats_exp(int on);
 enum GradPath : int { kPathAuto = -1, kPassClassic = 0, kPassWide = 1, kFusedWide = 2 };
 void set_grad_path(int path);                                    // kPathAuto (default): chosen per call
 GradPath grad_path_for(int D, int rows, bool plain_bf16);        // plain_bf16: bf16 store and bf16 io
+// Last chunk of a call with a bucketed dW reduction: 1 (default) = dX first on every SM when it does not overwrite x,
+// then the dW buckets beside the reductions; 0 = dW buckets first, dX beside the reductions.
+void set_tail_order(int order);
+int tail_order();
 
 // Optional per-kernel-class timing for benches: when enabled, run() brackets every launch with a pair of CUDA events on
 // the call's stream (the events are created when profiling is enabled, never inside a call). Classes: 0 logits,

@@ -45,89 +45,92 @@ __global__ void __launch_bounds__(kRowWarps * 32) k_rmsnorm_fwd(const __nv_bfloa
   }
 }
 
-// One CTA per part of consecutive rows; warp w takes rows r0 + w, r0 + w + kRowWarps, ... and keeps its gain-gradient
-// contributions in registers; the warps' sums are then added in warp order through shared memory.
-template <bool LEV, int NP>   // NP: 16-byte pieces a lane may own (D <= NP * 256)
-__global__ void __launch_bounds__(kRowWarps * 32) k_rmsnorm_bwd_add(const __nv_bfloat16* __restrict__ dy,
-                                                                 const __nv_bfloat16* __restrict__ x,
-                                                                 const __nv_bfloat16* __restrict__ gain,
-                                                                 const float* __restrict__ rstd,
-                                                                 const __nv_bfloat16* dres, __nv_bfloat16* dx,
-                                                                 float* __restrict__ partial, int64_t T, int D,
-                                                                 float eps, int64_t parts) {
-  extern __shared__ float sred[];   // [kRowWarps, D]
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// One CTA per part of consecutive rows (the partition of norm_partial_rows), row groups as described in ew_rows.cuh:
+// a thread loads its pieces of dy, x (and the residual gradient) once, the group reduces sum x^2 and sum x a, and the
+// same registers feed the output pass. Gain-gradient sums stay in the owning thread's registers for the whole part.
+template <bool LEV, int PP>
+__global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_rmsnorm_bwd_add(const __nv_bfloat16* __restrict__ dy,
+                                                                const __nv_bfloat16* __restrict__ x,
+                                                                const __nv_bfloat16* __restrict__ gain,
+                                                                const float* __restrict__ rstd,
+                                                                const __nv_bfloat16* dres, __nv_bfloat16* dx,
+                                                                float* __restrict__ partial, int64_t T, int D,
+                                                                float eps, int64_t parts, int G) {
+  __shared__ float red[2 * 8 * 2];
+  __shared__ float gsm[kGroupThreads * 8];
+  const RowGroup rg = row_group(G);
   const int pieces = D / 8;
-  const int my = (pieces - lane + 31) / 32;   // pieces this lane owns
+  int flip = 0;
+  uint4 gq[PP];
+#pragma unroll
+  for (int i = 0; i < PP; ++i) {
+    const int pc = rg.tg + i * rg.G;
+    gq[i] = pc < pieces ? ldg16(gain + pc * 8) : make_uint4(0u, 0u, 0u, 0u);
+  }
   for (int64_t p = blockIdx.x; p < parts; p += gridDim.x) {
     const int64_t r0 = p * T / parts, r1 = (p + 1) * T / parts;
-    float dg[NP][8];
+    float dg[PP][8];
 #pragma unroll
-    for (int i = 0; i < NP; ++i)
+    for (int i = 0; i < PP; ++i)
 #pragma unroll
       for (int e = 0; e < 8; ++e) dg[i][e] = 0.f;
-    for (int64_t row = r0 + warp; row < r1; row += kRowWarps) {
+    // every group runs the same number of iterations (the group reduction is a barrier of the group only, but the
+    // gain reduction at the end is a barrier of the CTA)
+    for (int64_t base = r0; base < r1; base += rg.groups) {
+      const int64_t row = base + rg.group;
+      const bool on = row < r1;
       const int64_t off = row * D;
-      float s_xx = 0.f, s_xa = 0.f;
-      for (int i = 0; i < my; ++i) {
-        const int c0 = (lane + 32 * i) * 8;
+      uint4 xq[PP], dq[PP], rq[PP];
+#pragma unroll
+      for (int i = 0; i < PP; ++i) {
+        const int pc = rg.tg + i * rg.G;
+        const bool in = on && pc < pieces;
+        xq[i] = in ? ldg16(x + off + pc * 8) : make_uint4(0u, 0u, 0u, 0u);
+        dq[i] = in ? ldg16(dy + off + pc * 8) : make_uint4(0u, 0u, 0u, 0u);
+        rq[i] = (in && dres) ? ldg16(dres + off + pc * 8) : make_uint4(0u, 0u, 0u, 0u);
+      }
+      float sums[2] = {0.f, 0.f};   // sum x^2, sum x a
+#pragma unroll
+      for (int i = 0; i < PP; ++i) {
         float xf[8], dyf[8], g[8];
-        load8(x + off + c0, xf);
-        load8(dy + off + c0, dyf);
-        load8(gain + c0, g);
+        unpack8(xq[i], xf);
+        unpack8(dq[i], dyf);
+        unpack8(gq[i], g);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const float a = LEV ? rb(__fmul_rn(g[e], dyf[e])) : g[e] * dyf[e];
-          s_xx = fmaf(xf[e], xf[e], s_xx);
-          s_xa = fmaf(xf[e], a, s_xa);
+          sums[0] = fmaf(xf[e], xf[e], sums[0]);
+          sums[1] = fmaf(xf[e], norm_a<LEV>(g[e], dyf[e]), sums[1]);
         }
       }
-      s_xx = warp_sum(s_xx);
-      s_xa = warp_sum(s_xa);
-      const float ms = __fdiv_rn(s_xx, float(D));
+      group_sum<2>(sums, rg, red, flip);
+      if (!on) continue;
+      const float ms = __fdiv_rn(sums[0], float(D));
       const float r = rstd ? __ldg(rstd + row) : rsqrtf(ms + eps);
-      const float c = __fdiv_rn(__fmul_rn(s_xa, __fmul_rn(-0.5f, __fdiv_rn(r, ms + eps))), float(D));
+      const float c2 = norm_c2(sums[1], r, ms, eps, D);
 #pragma unroll
-      for (int i = 0; i < NP; ++i) {
-        if (i < my) {
-          const int c0 = (lane + 32 * i) * 8;
+      for (int i = 0; i < PP; ++i) {
+        const int pc = rg.tg + i * rg.G;
+        if (pc < pieces) {
           float xf[8], dyf[8], g[8], d[8];
-          load8(x + off + c0, xf);
-          load8(dy + off + c0, dyf);
-          load8(gain + c0, g);
+          unpack8(xq[i], xf);
+          unpack8(dq[i], dyf);
+          unpack8(gq[i], g);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const float a = LEV ? rb(__fmul_rn(g[e], dyf[e])) : g[e] * dyf[e];
-            d[e] = LEV ? __fadd_rn(__fmul_rn(a, r), __fmul_rn(c, __fmul_rn(2.f, xf[e]))) : fmaf(a, r, c * (2.f * xf[e]));
-            dg[i][e] += LEV ? rb(__fmul_rn(dyf[e], rb(__fmul_rn(xf[e], r)))) : dyf[e] * (xf[e] * r);
+            d[e] = norm_dx<LEV>(norm_a<LEV>(g[e], dyf[e]), r, c2, xf[e]);
+            dg[i][e] += norm_gc<LEV>(dyf[e], xf[e], r);
           }
           if (dres) {
             float q[8];
-            load8(dres + off + c0, q);
+            unpack8(rq[i], q);
 #pragma unroll
             for (int e = 0; e < 8; ++e) d[e] = LEV ? __fadd_rn(q[e], rb(d[e])) : q[e] + d[e];
           }
-          store8(dx + off + c0, d);
+          *reinterpret_cast<uint4*>(dx + off + pc * 8) = pack8(d);
         }
       }
     }
-    if (partial) {
-#pragma unroll
-      for (int i = 0; i < NP; ++i)
-        if (i < my) {
-          const int c0 = (lane + 32 * i) * 8;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) sred[warp * D + c0 + e] = dg[i][e];
-        }
-      __syncthreads();
-      for (int d = threadIdx.x; d < D; d += kRowWarps * 32) {
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < kRowWarps; ++w) s = __fadd_rn(s, sred[w * D + d]);
-        partial[p * D + d] = s;
-      }
-      __syncthreads();
-    }
+    if (partial) write_gain_partial<PP>(dg, rg, pieces, gsm, partial + p * D);
   }
 }
 
@@ -156,20 +159,21 @@ void rmsnorm_bwd_add(const bf16_t* dy, const bf16_t* x, const bf16_t* gain, cons
                      bf16_t* dx, float* dgain_partial, int64_t T, int D, float eps, cudaStream_t st, Rounding r) {
   NM_REQUIRE(dy && x && gain && dx && T >= 0 && D > 0 && D % 8 == 0, "rmsnorm_bwd_add: dy, x, gain, dx, D % 8 == 0");
   NM_REQUIRE(aligned16(dy, x, gain, dres, dx, dgain_partial), "rmsnorm_bwd_add: every pointer must be 16-byte aligned");
-  NM_REQUIRE(D <= kMaxPieces * 32 * 8, "rmsnorm_bwd_add: D <= 8192");
+  NM_REQUIRE(D <= kGroupThreads * 4 * 8, "rmsnorm_bwd_add: D <= 8192");
   if (T == 0) return;
   const int64_t parts = norm_partial_rows(T);
-  const size_t smem = size_t(kRowWarps) * D * sizeof(float);
   const bool lev = r == Rounding::Levanter;
-  auto kern = D <= 512    ? (lev ? k_rmsnorm_bwd_add<true, 2> : k_rmsnorm_bwd_add<false, 2>)
-              : D <= 2048 ? (lev ? k_rmsnorm_bwd_add<true, 8> : k_rmsnorm_bwd_add<false, 8>)
-                          : (lev ? k_rmsnorm_bwd_add<true, kMaxPieces> : k_rmsnorm_bwd_add<false, kMaxPieces>);
-  NM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-  kern<<<int(parts), kRowWarps * 32, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(dy),
-                                              reinterpret_cast<const __nv_bfloat16*>(x),
-                                              reinterpret_cast<const __nv_bfloat16*>(gain), rstd,
-                                              reinterpret_cast<const __nv_bfloat16*>(dres),
-                                              reinterpret_cast<__nv_bfloat16*>(dx), dgain_partial, T, D, eps, parts);
+  const int pieces = D / 8;
+  const int pp = pieces <= kGroupThreads ? 1 : pieces <= 2 * kGroupThreads ? 2 : 4;
+  const int G = group_threads_for(pieces, pp);
+  auto kern = pp == 1   ? (lev ? k_rmsnorm_bwd_add<true, 1> : k_rmsnorm_bwd_add<false, 1>)
+              : pp == 2 ? (lev ? k_rmsnorm_bwd_add<true, 2> : k_rmsnorm_bwd_add<false, 2>)
+                        : (lev ? k_rmsnorm_bwd_add<true, 4> : k_rmsnorm_bwd_add<false, 4>);
+  kern<<<int(parts), kGroupThreads, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(dy),
+                                            reinterpret_cast<const __nv_bfloat16*>(x),
+                                            reinterpret_cast<const __nv_bfloat16*>(gain), rstd,
+                                            reinterpret_cast<const __nv_bfloat16*>(dres),
+                                            reinterpret_cast<__nv_bfloat16*>(dx), dgain_partial, T, D, eps, parts, G);
   NM_CUDA(cudaGetLastError());
 }
 

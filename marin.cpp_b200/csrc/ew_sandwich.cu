@@ -4,7 +4,8 @@
 // src/kernels/elementwise/rmsnorm_kernels.cuh:100-235 (k_sandwich_fwd / k_sandwich_bwd):
 //   forward   y = g_post ? norm(branch; g_post) : branch;  x_out = bf16(x_in + y);  a_next = norm(x_out; g_next)
 //   backward  dx_mid = dx_out + norm_next_bwd(da_next);  dx_in = dx_mid;  dbranch = g_post ? norm_post_bwd(dx_mid) : dx_mid
-// with the levanter rounding points of ew_api.hpp (or f32 chains under accurate rounding). One warp per row.
+// with the levanter rounding points of ew_api.hpp (or f32 chains under accurate rounding). Forward: one warp per row;
+// backward: the row-group geometry of ew_rows.cuh.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -81,68 +82,94 @@ __global__ void __launch_bounds__(kRowWarps * 32) k_sandwich_fwd(const __nv_bflo
   }
 }
 
-// One CTA per part of consecutive rows (the partition of norm_partial_rows); warp w takes rows r0 + w, r0 + w + 8, ...
-// Gain contributions stay in registers per lane and are added across the warps in warp order at the end.
-template <bool LEV, int NP>
-__global__ void __launch_bounds__(kRowWarps * 32) k_sandwich_bwd(const __nv_bfloat16* dx_out,
-                                                                 const __nv_bfloat16* __restrict__ da_next,
-                                                                 const __nv_bfloat16* __restrict__ x_out,
-                                                                 const __nv_bfloat16* __restrict__ g_next,
-                                                                 const float* __restrict__ rstd_next,
-                                                                 const __nv_bfloat16* __restrict__ branch,
-                                                                 const __nv_bfloat16* __restrict__ g_post,
-                                                                 const float* __restrict__ rstd_post,
-                                                                 __nv_bfloat16* dx_in, __nv_bfloat16* dbranch,
-                                                                 float* __restrict__ pg_next,
-                                                                 float* __restrict__ pg_post, int64_t T, int D,
-                                                                 float eps, int64_t parts) {
-  extern __shared__ float sred[];   // [kRowWarps, D]
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// One CTA per part of consecutive rows (the partition of norm_partial_rows), row groups as described in ew_rows.cuh.
+// A thread loads its pieces of x_out, da_next, dx_out and branch once; the group reduces sum x_out^2, sum x_out a and
+// sum branch^2 together, the middle gradient dx_mid is formed and stored, the group reduces sum branch a_post, and
+// the branch gradient follows from the registers that are still there. Gain-gradient sums of both norms stay in the
+// owning thread's registers for the whole part.
+template <bool LEV, int PP>
+__global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_sandwich_bwd(const __nv_bfloat16* dx_out,
+                                                             const __nv_bfloat16* __restrict__ da_next,
+                                                             const __nv_bfloat16* __restrict__ x_out,
+                                                             const __nv_bfloat16* __restrict__ g_next,
+                                                             const float* __restrict__ rstd_next,
+                                                             const __nv_bfloat16* __restrict__ branch,
+                                                             const __nv_bfloat16* __restrict__ g_post,
+                                                             const float* __restrict__ rstd_post,
+                                                             __nv_bfloat16* dx_in, __nv_bfloat16* dbranch,
+                                                             float* __restrict__ pg_next,
+                                                             float* __restrict__ pg_post, int64_t T, int D,
+                                                             float eps, int64_t parts, int G) {
+  __shared__ float red[2 * 8 * 3];
+  __shared__ float gsm[kGroupThreads * 8];
+  const RowGroup rg = row_group(G);
   const int pieces = D / 8;
-  const int my = (pieces - lane + 31) / 32;
+  const bool post = g_post != nullptr;
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  int flip = 0;
+  uint4 gnq[PP], gpq[PP];
+#pragma unroll
+  for (int i = 0; i < PP; ++i) {
+    const int pc = rg.tg + i * rg.G;
+    gnq[i] = pc < pieces ? ldg16(g_next + pc * 8) : zero4;
+    gpq[i] = (post && pc < pieces) ? ldg16(g_post + pc * 8) : zero4;
+  }
   for (int64_t p = blockIdx.x; p < parts; p += gridDim.x) {
     const int64_t r0 = p * T / parts, r1 = (p + 1) * T / parts;
-    float dgn[NP][8], dgp[NP][8];
+    float dgn[PP][8], dgp[PP][8];
 #pragma unroll
-    for (int i = 0; i < NP; ++i)
+    for (int i = 0; i < PP; ++i)
 #pragma unroll
       for (int e = 0; e < 8; ++e) dgn[i][e] = dgp[i][e] = 0.f;
-    for (int64_t row = r0 + warp; row < r1; row += kRowWarps) {
+    for (int64_t base = r0; base < r1; base += rg.groups) {
+      const int64_t row = base + rg.group;
+      const bool on = row < r1;
       const int64_t off = row * D;
-      float s_xx = 0.f, s_xa = 0.f, s_bb = 0.f;
-      for (int i = 0; i < my; ++i) {
-        const int c0 = (lane + 32 * i) * 8;
-        float xo[8], da[8], g[8];
-        load8(x_out + off + c0, xo);
-        load8(da_next + off + c0, da);
-        load8(g_next + c0, g);
+      uint4 xq[PP], aq[PP], oq[PP], bq[PP];
+#pragma unroll
+      for (int i = 0; i < PP; ++i) {
+        const int pc = rg.tg + i * rg.G;
+        const bool in = on && pc < pieces;
+        xq[i] = in ? ldg16(x_out + off + pc * 8) : zero4;
+        aq[i] = in ? ldg16(da_next + off + pc * 8) : zero4;
+        oq[i] = in ? ldg16(dx_out + off + pc * 8) : zero4;
+        bq[i] = (in && post) ? ldg16(branch + off + pc * 8) : zero4;
+      }
+      float sums[3] = {0.f, 0.f, 0.f};   // sum x_out^2, sum x_out a_next, sum branch^2
+#pragma unroll
+      for (int i = 0; i < PP; ++i) {
+        float xo[8], da[8], g[8], b[8];
+        unpack8(xq[i], xo);
+        unpack8(aq[i], da);
+        unpack8(gnq[i], g);
+        unpack8(bq[i], b);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          s_xx = fmaf(xo[e], xo[e], s_xx);
-          s_xa = fmaf(xo[e], norm_a<LEV>(g[e], da[e]), s_xa);
-        }
-        if (g_post) {
-          float b[8];
-          load8(branch + off + c0, b);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) s_bb = fmaf(b[e], b[e], s_bb);
+          sums[0] = fmaf(xo[e], xo[e], sums[0]);
+          sums[1] = fmaf(xo[e], norm_a<LEV>(g[e], da[e]), sums[1]);
+          sums[2] = fmaf(b[e], b[e], sums[2]);
         }
       }
-      s_xx = warp_sum(s_xx);
-      s_xa = warp_sum(s_xa);
-      const float ms_n = __fdiv_rn(s_xx, float(D));
-      const float r_n = rstd_next ? __ldg(rstd_next + row) : rsqrtf(ms_n + eps);
-      const float c2n = norm_c2(s_xa, r_n, ms_n, eps, D);
-      float s_bap = 0.f;
+      group_sum<3>(sums, rg, red, flip);
+      float r_n = 0.f, c2n = 0.f;
+      if (on) {
+        const float ms_n = __fdiv_rn(sums[0], float(D));
+        r_n = rstd_next ? __ldg(rstd_next + row) : rsqrtf(ms_n + eps);
+        c2n = norm_c2(sums[1], r_n, ms_n, eps, D);
+      }
+      // the middle gradient: stored as dx_in, kept (rounded to bf16, as stored) for the post-norm backward
+      uint4 mq[PP];
+      float bap[1] = {0.f};
 #pragma unroll
-      for (int i = 0; i < NP; ++i) {
-        if (i < my) {
-          const int c0 = (lane + 32 * i) * 8;
+      for (int i = 0; i < PP; ++i) {
+        const int pc = rg.tg + i * rg.G;
+        mq[i] = zero4;
+        if (on && pc < pieces) {
           float xo[8], da[8], g[8], dxo[8], dxm[8];
-          load8(x_out + off + c0, xo);
-          load8(da_next + off + c0, da);
-          load8(g_next + c0, g);
-          load8(dx_out + off + c0, dxo);
+          unpack8(xq[i], xo);
+          unpack8(aq[i], da);
+          unpack8(gnq[i], g);
+          unpack8(oq[i], dxo);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const float a = norm_a<LEV>(g[e], da[e]);
@@ -150,63 +177,47 @@ __global__ void __launch_bounds__(kRowWarps * 32) k_sandwich_bwd(const __nv_bflo
             dgn[i][e] += norm_gc<LEV>(da[e], xo[e], r_n);
             dxm[e] = rb(LEV ? __fadd_rn(dxo[e], rb(dxn)) : dxo[e] + dxn);
           }
-          store8(dx_in + off + c0, dxm);
-          if (g_post) {
+          mq[i] = pack8(dxm);
+          *reinterpret_cast<uint4*>(dx_in + off + pc * 8) = mq[i];
+          if (post) {
             float b[8], gp[8];
-            load8(branch + off + c0, b);
-            load8(g_post + c0, gp);
+            unpack8(bq[i], b);
+            unpack8(gpq[i], gp);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) s_bap = fmaf(b[e], norm_a<LEV>(gp[e], dxm[e]), s_bap);
+            for (int e = 0; e < 8; ++e) bap[0] = fmaf(b[e], norm_a<LEV>(gp[e], dxm[e]), bap[0]);
           } else if (dbranch != dx_in) {
-            store8(dbranch + off + c0, dxm);
+            *reinterpret_cast<uint4*>(dbranch + off + pc * 8) = mq[i];
           }
         }
       }
-      if (g_post) {
-        s_bb = warp_sum(s_bb);
-        s_bap = warp_sum(s_bap);
-        const float ms_p = __fdiv_rn(s_bb, float(D));
-        const float r_p = rstd_post ? __ldg(rstd_post + row) : rsqrtf(ms_p + eps);
-        const float c2p = norm_c2(s_bap, r_p, ms_p, eps, D);
+      if (post) {   // uniform over the CTA
+        group_sum<1>(bap, rg, red, flip);
+        if (on) {
+          const float ms_p = __fdiv_rn(sums[2], float(D));
+          const float r_p = rstd_post ? __ldg(rstd_post + row) : rsqrtf(ms_p + eps);
+          const float c2p = norm_c2(bap[0], r_p, ms_p, eps, D);
 #pragma unroll
-        for (int i = 0; i < NP; ++i) {
-          if (i < my) {
-            const int c0 = (lane + 32 * i) * 8;
-            float b[8], gp[8], dxm[8], db[8];
-            load8(branch + off + c0, b);
-            load8(g_post + c0, gp);
-            load8(dx_in + off + c0, dxm);   // this lane's own writes of the pass above
+          for (int i = 0; i < PP; ++i) {
+            const int pc = rg.tg + i * rg.G;
+            if (pc < pieces) {
+              float b[8], gp[8], dxm[8], db[8];
+              unpack8(bq[i], b);
+              unpack8(gpq[i], gp);
+              unpack8(mq[i], dxm);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float ap = norm_a<LEV>(gp[e], dxm[e]);
-              db[e] = norm_dx<LEV>(ap, r_p, c2p, b[e]);
-              dgp[i][e] += norm_gc<LEV>(dxm[e], b[e], r_p);
+              for (int e = 0; e < 8; ++e) {
+                const float ap = norm_a<LEV>(gp[e], dxm[e]);
+                db[e] = norm_dx<LEV>(ap, r_p, c2p, b[e]);
+                dgp[i][e] += norm_gc<LEV>(dxm[e], b[e], r_p);
+              }
+              *reinterpret_cast<uint4*>(dbranch + off + pc * 8) = pack8(db);
             }
-            store8(dbranch + off + c0, db);
           }
         }
       }
     }
-    // partial rows of the gain gradients: warps added in warp order
-    for (int which = 0; which < 2; ++which) {
-      float* out = which == 0 ? pg_next : pg_post;
-      if (!out || (which == 1 && !g_post)) continue;
-#pragma unroll
-      for (int i = 0; i < NP; ++i)
-        if (i < my) {
-          const int c0 = (lane + 32 * i) * 8;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) sred[warp * D + c0 + e] = which == 0 ? dgn[i][e] : dgp[i][e];
-        }
-      __syncthreads();
-      for (int d = threadIdx.x; d < D; d += kRowWarps * 32) {
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < kRowWarps; ++w) s = __fadd_rn(s, sred[w * D + d]);
-        out[p * D + d] = s;
-      }
-      __syncthreads();
-    }
+    if (pg_next) write_gain_partial<PP>(dgn, rg, pieces, gsm, pg_next + p * D);
+    if (pg_post && post) write_gain_partial<PP>(dgp, rg, pieces, gsm, pg_post + p * D);
   }
 }
 
@@ -241,20 +252,20 @@ void sandwich_tail_bwd(const bf16_t* dx_out, const bf16_t* da_next, const bf16_t
   NM_REQUIRE(aligned16(dx_out, da_next, x_out, g_next, branch, g_post, dx_in, dbranch, pg_next, pg_post),
              "sandwich_tail_bwd: every row pointer must be 16-byte aligned");
   NM_REQUIRE(!g_post || branch, "sandwich_tail_bwd: a post-norm needs the branch output");
-  NM_REQUIRE(D <= kMaxPieces * 32 * 8, "sandwich_tail_bwd: D <= 8192");
+  NM_REQUIRE(D <= kGroupThreads * 4 * 8, "sandwich_tail_bwd: D <= 8192");
   if (T == 0) return;
   const int64_t parts = norm_partial_rows(T);
-  const size_t smem = size_t(kRowWarps) * D * sizeof(float);
   const bool lev = r == Rounding::Levanter;
-  auto kern = D <= 512    ? (lev ? k_sandwich_bwd<true, 2> : k_sandwich_bwd<false, 2>)
-              : D <= 2048 ? (lev ? k_sandwich_bwd<true, 8> : k_sandwich_bwd<false, 8>)
-                          : (lev ? k_sandwich_bwd<true, kMaxPieces> : k_sandwich_bwd<false, kMaxPieces>);
-  NM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  const int pieces = D / 8;
+  const int pp = pieces <= kGroupThreads ? 1 : pieces <= 2 * kGroupThreads ? 2 : 4;
+  const int G = group_threads_for(pieces, pp);
+  auto kern = pp == 1   ? (lev ? k_sandwich_bwd<true, 1> : k_sandwich_bwd<false, 1>)
+              : pp == 2 ? (lev ? k_sandwich_bwd<true, 2> : k_sandwich_bwd<false, 2>)
+                        : (lev ? k_sandwich_bwd<true, 4> : k_sandwich_bwd<false, 4>);
   auto B = [](const bf16_t* p) { return reinterpret_cast<const __nv_bfloat16*>(p); };
   auto M = [](bf16_t* p) { return reinterpret_cast<__nv_bfloat16*>(p); };
-  kern<<<int(parts), kRowWarps * 32, smem, st>>>(B(dx_out), B(da_next), B(x_out), B(g_next), rstd_next, B(branch),
-                                                 B(g_post), rstd_post, M(dx_in), M(dbranch), pg_next, pg_post, T, D, eps,
-                                                 parts);
+  kern<<<int(parts), kGroupThreads, 0, st>>>(B(dx_out), B(da_next), B(x_out), B(g_next), rstd_next, B(branch), B(g_post),
+                                            rstd_post, M(dx_in), M(dbranch), pg_next, pg_post, T, D, eps, parts, G);
   NM_CUDA(cudaGetLastError());
 }
 

@@ -39,6 +39,7 @@ SIGS = {
     "nm_ce_suggest_chunk_rows": (I32, [I64]),
     "nm_ce_test_gemm": (I32, [I32, VP, I64, VP, I64, VP, I64, I32, I32, I32, VP, VP, VP]),
     "nm_ce_set_grad_path": (I32, [I32]),
+    "nm_ce_set_tail_order": (I32, [I32]),
     "nm_ce_sampled_stride": (I64, [I64]),
     "nm_ce_sampled_workspace_bytes": (U64, [I64, I32, I32, I32, I32, I32]),
     "nm_ce_sampled_head": (I32, [I32, I32, VP, VP, VP, VP, VP, VP, VP, VP, VP, I32, VP, I32, I64, I32, I32, I32, I64, I32,

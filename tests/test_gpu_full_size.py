@@ -308,6 +308,18 @@ def test_one_rank_reducer_attached_to_the_call():
                 assert same_bits(got[i], plain[i]), f"reduce dtype {reduce_dtype}: {name} differs from the plain call"
             want = plain[3] if reduce_dtype == 0 else plain[3].to(torch.bfloat16).float()
             assert same_bits(dw, want), f"reduce dtype {reduce_dtype}: dW differs"
+        # dX written over x keeps the dW-first order of the last chunk; the other order (dX first) ran above
+        dw = torch.zeros(V, D, dtype=torch.float32, device="cuda")
+        red = ctypes.c_void_p()
+        lib().nm_grad_reducer_create(comm, nmce.ptr(dw), V, D, 5, 0, None, ctypes.byref(red))
+        try:
+            xi = X.clone()
+            run_ce(xi, W, Y, WT, gs, chunk=chunk, z_loss=1e-4, dx=xi, dw=dw, reducer=red)
+            lib().nm_grad_reducer_wait(red, None)
+            torch.cuda.synchronize()
+        finally:
+            lib().nm_grad_reducer_destroy(red)
+        assert same_bits(xi, plain[2]) and same_bits(dw, plain[3]), "dx == x with a reducer differs from the plain call"
     finally:
         lib().nm_comm_destroy(comm)
 
