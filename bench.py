@@ -153,15 +153,28 @@ def cpu_sample(cfg, seconds=12.0, rows0=32):
 
 REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libref_ce.so")
 
-# DRAM bytes (read + write) one launch of each tcgen05 kernel moves per row of its chunk, at vocabulary 128256, from
-# hardware-counter captures of small cases of the same kernels (one kernel, a few launches), which grow in proportion
-# to the rows: {hidden: {kernel: bytes per row}}. None where no capture exists.
-DRAM_BYTES_PER_ROW = {}
+# DRAM bytes (read + write) per launch of the dominant tensor-core kernel, from hardware counters
+# (dram__bytes_read.sum + dram__bytes_write.sum). Hidden 2048 (128 x 256-tile kernels, unchanged since): one capture of
+# full chunks, {chunk rows: {kernel: bytes}}. Other shapes: the ratio of measured to algorithmic bytes seen on a small
+# case (one chunk of 4096 rows), applied to the algorithmic bytes of a full launch.
+FULL_SIZE_TRAFFIC = {(2048, 128256, 18944): {"logits": 7.60e9, "dw": 11.34e9, "dx": 9.26e9},
+                     (2048, 128256, 16384): {"logits": 6.40e9, "dw": 10.07e9, "dx": 8.04e9}}
+SMALL_CASE_RATIO = {(1024, 128256): {"logits": 0.97, "dw": 0.98, "dx": 1.07},
+                    (512, 128256): {"logits": 0.96, "dw": 0.98, "dx": 1.00}}
 
 
 def dram_traffic_per_launch(kernel, D, V, chunk, grad_path):
-    per_row = DRAM_BYTES_PER_ROW.get((D, V, grad_path), {}).get(kernel)
-    return None if per_row is None else per_row * chunk
+    full = FULL_SIZE_TRAFFIC.get((D, V, chunk), {}).get(kernel)
+    if full is not None and grad_path in (-1, 0):
+        return full
+    ratio = SMALL_CASE_RATIO.get((D, V), {}).get(kernel)
+    if ratio is None or grad_path not in (-1, 2):
+        return None
+    store = 2.0 * chunk * V
+    algorithmic = {"logits": 2.0 * chunk * D + 2.0 * V * D + store + 8.0 * chunk * ((V + 255) // 256),
+                   "dw": store + 2.0 * chunk * D + 8.0 * V * D,
+                   "dx": store + 2.0 * V * D + 2.0 * chunk * D}[kernel]
+    return ratio * algorithmic
 
 
 def reference_arm_gpu(args, cfg):
@@ -614,6 +627,9 @@ def main():
                     help="statistics and loss only (the evaluation path; also the small case of the logits kernel without its store)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input leg")
+    ap.add_argument("--adjacent-only", action="store_true",
+                    help="time only the memory-bound neighbours (RMSNorm pair, sandwich tail, in-place pass, AdamH) and "
+                         "print their JSON: a small case of those kernels for profiling")
     ap.add_argument("--no-others", action="store_true",
                     help="skip the short runs of the other configurations and of the neighbouring memory-bound kernels")
     args = ap.parse_args()
@@ -650,6 +666,9 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     env = dict(torch=torch, nmce=nmce, lib=lib, dist=dist, rank=rank, world=world, dev=dev, local_rank=local_rank)
+    if args.adjacent_only:
+        print(json.dumps({"adjacent": adjacent_kernels(env, args.tokens or 65536, cfg["D"])}))
+        return
     if world > 1:
         idbuf = torch.zeros(128, dtype=torch.uint8)
         if rank == 0:

@@ -9,7 +9,7 @@
 namespace nm::ew {
 
 constexpr int kRowWarps = 8;      // warps per CTA in the row kernels
-constexpr int kMaxPieces = 32;    // 16-byte pieces a lane may own: D <= 32 * 32 * 8 = 8192
+
 
 __device__ __forceinline__ float rb(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ float warp_sum(float v) {

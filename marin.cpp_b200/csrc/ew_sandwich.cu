@@ -100,13 +100,14 @@ __global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_sandwich_bwd
                                                              float* __restrict__ pg_next,
                                                              float* __restrict__ pg_post, int64_t T, int D,
                                                              float eps, int64_t parts, int G) {
-  __shared__ float red[2 * 8 * 3];
+  __shared__ float red[2 * 8 * 3];    // the three-value reduction of every row
+  __shared__ float red1[2 * 8 * 1];   // the one-value reduction that follows it: buffers of its own, flips of its own
   __shared__ float gsm[kGroupThreads * 8];
   const RowGroup rg = row_group(G);
   const int pieces = D / 8;
   const bool post = g_post != nullptr;
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-  int flip = 0;
+  int flip = 0, flip1 = 0;
   uint4 gnq[PP], gpq[PP];
 #pragma unroll
   for (int i = 0; i < PP; ++i) {
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_sandwich_bwd
         }
       }
       if (post) {   // uniform over the CTA
-        group_sum<1>(bap, rg, red, flip);
+        group_sum<1>(bap, rg, red1, flip1);
         if (on) {
           const float ms_p = __fdiv_rn(sums[2], float(D));
           const float r_p = rstd_post ? __ldg(rstd_post + row) : rsqrtf(ms_p + eps);
