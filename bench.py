@@ -546,6 +546,7 @@ def adjacent_kernels(env, tokens=65536, hidden=2048):
     x = torch.randn(T, D, generator=g, device="cuda").to(bf)
     b = torch.randn(T, D, generator=g, device="cuda").to(bf)
     dy = (torch.randn(T, D, generator=g, device="cuda") * 1e-2).to(bf)
+    dy2 = (torch.randn(T, D, generator=g, device="cuda") * 1e-2).to(bf)
     gain = torch.ones(D, dtype=bf, device="cuda")
     y, y2, y3 = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
     rstd, rstd2 = torch.empty(T, device="cuda"), torch.empty(T, device="cuda")
@@ -576,7 +577,7 @@ def adjacent_kernels(env, tokens=65536, hidden=2048):
           lambda: lib.nm_sandwich_tail_fwd(1, 0, p(b), p(x), p(gain), p(gain), p(y), p(y2), p(rstd), p(rstd2), T, D,
                                            1e-5, None))
     timed("sandwich_tail_bwd", 6 * TD2,
-          lambda: lib.nm_sandwich_tail_bwd(1, 0, p(dy), p(dy), p(y), p(gain), p(rstd2), p(b), p(gain), p(rstd), p(y3),
+          lambda: lib.nm_sandwich_tail_bwd(1, 0, p(dy), p(dy2), p(y), p(gain), p(rstd2), p(b), p(gain), p(rstd), p(y3),
                                            p(y2), None, None, T, D, 1e-5, None))
     V, Rr = 128256, 4096
     store = torch.randn(Rr, V, generator=g, device="cuda").to(bf)

@@ -20,6 +20,12 @@ int nm_rmsnorm_bwd_add_partial(int dtype, int rounding, const void* dy, const vo
                                const float* rstd, const void* dres, void* dx, float* dgain_partial, int64_t T, int D,
                                float eps, void* stream);
 
+/* The norm backward kernels (nm_rmsnorm_bwd_add, nm_rmsnorm_bwd_add_partial, nm_sandwich_tail_bwd) stage their operands
+ * through a ring in shared memory whose waits are bounded; one that ran out leaves a bit in a per-GPU word built into the
+ * library. This reads the word after the stream's work (it synchronises the stream), clears it when set, and returns
+ * NM_ERR_DEVICE with the bits in *status_host when it was not 0. */
+int nm_norm_bwd_device_status(void* stream, uint32_t* status_host);
+
 #ifdef __cplusplus
 }
 #endif

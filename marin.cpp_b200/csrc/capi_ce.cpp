@@ -337,6 +337,15 @@ int nm_doc_meta(const int32_t* tokens, const uint8_t* row_valid, int rows, int S
                      row_seg_start, overflow, S(stream));
   });
 }
+int nm_norm_bwd_device_status(void* stream, uint32_t* status_host) {
+  return guarded([&] {
+    NM_REQUIRE(status_host != nullptr, "nm_norm_bwd_device_status: status_host is required");
+    *status_host = nm::ew::read_row_status(S(stream));
+    if (*status_host != 0)
+      throw nm::DeviceError("norm backward: a bounded device-side wait ran out (status bits " +
+                            std::to_string(*status_host) + "); the gradients of that call are invalid");
+  });
+}
 int nm_sum_fixed(const float* x, int64_t n, float* out, void* stream) {
   return guarded([&] { nm::ew::sum_fixed(x, n, out, S(stream)); });
 }

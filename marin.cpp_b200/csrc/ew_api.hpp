@@ -44,6 +44,12 @@ void sandwich_tail_bwd(const bf16_t* dx_out, const bf16_t* da_next, const bf16_t
                        bf16_t* dx_in, bf16_t* dbranch, float* pg_next, float* pg_post, int64_t T, int D, float eps,
                        cudaStream_t st, Rounding r = Rounding::Levanter);
 
+// The word the norm backward kernels OR their error bits into when one of their bounded waits runs out (one per GPU,
+// zero-initialised, address looked up on first use: make the first backward call on a device outside a stream capture).
+// read_row_status copies it to the host after the stream's work, clears it when set, and returns it.
+uint32_t* row_status_word();
+uint32_t read_row_status(cudaStream_t st);
+
 // Microbatch metadata from token rows [rows, S] (ew_misc.cu): targets (next token; the last position wraps and has
 // weight 0), weight (0 for an invalid row), pos, per-row segment starts [rows, max_segs + 1] (padded with S), packed
 // cu_seqlens [rows * max_segs + 1] (padded with rows * S), the segment count, and an overflow flag set when a row

@@ -7,12 +7,19 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <mutex>
 
 #include "ce_internal.hpp"
 #include "ew_api.hpp"
 
 namespace nm::ew {
 namespace {
+
+// Where the row kernels whose waits are bounded (the norm backward kernels' batch ring) leave their error bits: one word
+// per GPU, built into the library because those entry points take no workspace.
+static __device__ uint32_t g_row_status_word;
+std::mutex g_row_status_mu;
+uint32_t* g_row_status_ptr[kMaxDeviceOrdinals] = {};
 
 constexpr int kMetaThreads = 256;
 
@@ -151,6 +158,26 @@ void doc_meta(const int32_t* tokens, const uint8_t* row_valid, int rows, int S, 
   NM_CUDA(cudaGetLastError());
   k_doc_meta_pack<<<1, 1024, 0, st>>>(row_seg_start, rows, S, max_segs, cu_seqlens, n_segs);
   NM_CUDA(cudaGetLastError());
+}
+
+uint32_t* row_status_word() {
+  const int dev = current_device_info().ordinal;
+  std::lock_guard<std::mutex> lk(g_row_status_mu);
+  if (!g_row_status_ptr[dev]) {
+    void* p = nullptr;
+    NM_CUDA(cudaGetSymbolAddress(&p, g_row_status_word));
+    g_row_status_ptr[dev] = static_cast<uint32_t*>(p);
+  }
+  return g_row_status_ptr[dev];
+}
+
+uint32_t read_row_status(cudaStream_t st) {
+  uint32_t word = 0;
+  uint32_t* dev = row_status_word();
+  NM_CUDA(cudaMemcpyAsync(&word, dev, sizeof(word), cudaMemcpyDeviceToHost, st));
+  NM_CUDA(cudaStreamSynchronize(st));
+  if (word != 0) NM_CUDA(cudaMemsetAsync(dev, 0, sizeof(word), st));
+  return word;
 }
 
 void sum_fixed(const float* x, int64_t n, float* out, cudaStream_t st) {

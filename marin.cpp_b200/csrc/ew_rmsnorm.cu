@@ -45,21 +45,52 @@ __global__ void __launch_bounds__(kRowWarps * 32) k_rmsnorm_fwd(const __nv_bfloa
   }
 }
 
-// One CTA per part of consecutive rows (the partition of norm_partial_rows), row groups as described in ew_rows.cuh:
-// a thread loads its pieces of dy, x (and the residual gradient) once, the group reduces sum x^2 and sum x a, and the
-// same registers feed the output pass. Gain-gradient sums stay in the owning thread's registers for the whole part.
+// A CTA walks parts of consecutive rows (the partition of norm_partial_rows) in batches, row groups and batch ring as
+// described in ew_rows.cuh: a thread takes its pieces of dy, x (and the residual gradient) from the landed batch into
+// registers, the group reduces sum x^2 and sum x a, and the same registers feed the output pass. Gain-gradient sums stay
+// in the owning thread's registers for the whole part.
 template <bool LEV, int PP>
-__global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_rmsnorm_bwd_add(const __nv_bfloat16* __restrict__ dy,
-                                                                const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_rmsnorm_bwd_add(const __nv_bfloat16* dy,
+                                                                const __nv_bfloat16* x,
                                                                 const __nv_bfloat16* __restrict__ gain,
                                                                 const float* __restrict__ rstd,
                                                                 const __nv_bfloat16* dres, __nv_bfloat16* dx,
                                                                 float* __restrict__ partial, int64_t T, int D,
-                                                                float eps, int64_t parts, int G) {
-  __shared__ float red[2 * 8 * 2];
-  __shared__ float gsm[kGroupThreads * 8];
+                                                                float eps, int64_t parts, int G, int stages,
+                                                                uint32_t op_bytes, float inv_n, uint32_t* status) {
+  using namespace nm::ptx;
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  __shared__ __align__(16) float red[2 * 8 * 2];
+  __shared__ __align__(16) float gsm[kGroupThreads * 4];
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
   const RowGroup rg = row_group(G);
   const int pieces = D / 8;
+  RowRing ring;
+  ring.data = (smem_u32(ring_raw) + 127u) & ~127u;
+  ring.op_bytes = op_bytes, ring.stages = stages, ring.nops = dres ? 3 : 2;
+  ring.full = ring.data + uint32_t(stages * ring.nops) * op_bytes;
+  ring.empty = ring.full + 8u * stages;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(ring.full + 8u * s, 1), mbar_init(ring.empty + 8u * s, kRingWarps);
+    abort_word = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  auto fetch = [&](int s, const BatchWalk& b) {   // thread 0: one batch of every operand into slot s
+    const uint32_t bytes = b.rows(rg.groups) * uint32_t(D) * 2u;
+    const uint32_t bar = ring.full + 8u * s;
+    mbar_arrive_expect_tx(bar, bytes * ring.nops);
+    bulk_load(ring.slot(s, 0), dy + b.row * D, bytes, bar);
+    bulk_load(ring.slot(s, 1), x + b.row * D, bytes, bar);
+    if (dres) bulk_load(ring.slot(s, 2), dres + b.row * D, bytes, bar);
+  };
+  BatchWalk w, ahead;
+  w.begin(T, parts);
+  ahead = w;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages - 1 && !ahead.done(parts); ++s, ahead.next(rg.groups, T, parts)) fetch(s, ahead);
+  }
   int flip = 0;
   uint4 gq[PP];
 #pragma unroll
@@ -67,34 +98,44 @@ __global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_rmsnorm_bwd_
     const int pc = rg.tg + i * rg.G;
     gq[i] = pc < pieces ? ldg16(gain + pc * 8) : make_uint4(0u, 0u, 0u, 0u);
   }
-  for (int64_t p = blockIdx.x; p < parts; p += gridDim.x) {
-    const int64_t r0 = p * T / parts, r1 = (p + 1) * T / parts;
-    float dg[PP][8];
+  F2 dg[PP][4];   // gain-gradient sums of this thread's columns, two per register pair
 #pragma unroll
-    for (int i = 0; i < PP; ++i)
+  for (int i = 0; i < PP; ++i)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) dg[i][e] = 0.f;
-    // every group runs the same number of iterations (the group reduction is a barrier of the group only, but the
-    // gain reduction at the end is a barrier of the CTA)
-    for (int64_t base = r0; base < r1; base += rg.groups) {
-      const int64_t row = base + rg.group;
-      const bool on = row < r1;
-      const int64_t off = row * D;
-      uint4 xq[PP], dq[PP], rq[PP];
+    for (int q = 0; q < 4; ++q) dg[i][q] = f2(0.f, 0.f);
+  // every group runs every batch (the group reduction is a barrier of the group only, but the slot hand-back counts all
+  // warps and the gain reduction at the end of a part is a barrier of the CTA)
+  int s = 0;
+  uint32_t phase = 0;
+  for (; !w.done(parts); w.next(rg.groups, T, parts)) {
+    const int64_t row = w.row + rg.group;
+    const bool on = row < w.end;
+    const int64_t off = row * D;
+    const float r_in = (on && rstd) ? __ldg(rstd + row) : 0.f;   // asked for before the wait: lands with the batch
+    mbar_wait<true>(ring.full + 8u * s, phase, abort_flag, status, kErrTransformWait);
+    // a thread's pieces of the landed batch are read from the slot where a pass needs them (0 past the row's end)
+    const uint32_t at0 = ring.slot(s, 0) + uint32_t(rg.group * D + rg.tg * 8) * 2u;
+    auto piece = [&](int op, int i) {
+      const int pc = rg.tg + i * rg.G;
+      return (on && pc < pieces) ? ld_shared_v4(at0 + uint32_t(op) * op_bytes + uint32_t(i * rg.G) * 16u)
+                                 : make_uint4(0u, 0u, 0u, 0u);
+    };
+    float sums[2] = {0.f, 0.f};   // sum x^2, sum x a
+    F2 sxx = f2(0.f, 0.f), sxa = sxx;   // levanter: even and odd elements summed apart, two per instruction
 #pragma unroll
-      for (int i = 0; i < PP; ++i) {
-        const int pc = rg.tg + i * rg.G;
-        const bool in = on && pc < pieces;
-        xq[i] = in ? ldg16(x + off + pc * 8) : make_uint4(0u, 0u, 0u, 0u);
-        dq[i] = in ? ldg16(dy + off + pc * 8) : make_uint4(0u, 0u, 0u, 0u);
-        rq[i] = (in && dres) ? ldg16(dres + off + pc * 8) : make_uint4(0u, 0u, 0u, 0u);
-      }
-      float sums[2] = {0.f, 0.f};   // sum x^2, sum x a
+    for (int i = 0; i < PP; ++i) {
+      const uint4 dqi = piece(0, i), xqi = piece(1, i);
+      if constexpr (LEV) {
 #pragma unroll
-      for (int i = 0; i < PP; ++i) {
+        for (int q = 0; q < 4; ++q) {
+          const F2 xx = f2_of(word_of(xqi, q)), aa = f2_of(mul_bf16x2(word_of(gq[i], q), word_of(dqi, q)));
+          sxx = f2_fma(xx, xx, sxx);
+          sxa = f2_fma(xx, aa, sxa);
+        }
+      } else {
         float xf[8], dyf[8], g[8];
-        unpack8(xq[i], xf);
-        unpack8(dq[i], dyf);
+        unpack8(xqi, xf);
+        unpack8(dqi, dyf);
         unpack8(gq[i], g);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -102,36 +143,79 @@ __global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_rmsnorm_bwd_
           sums[1] = fmaf(xf[e], norm_a<LEV>(g[e], dyf[e]), sums[1]);
         }
       }
-      group_sum<2>(sums, rg, red, flip);
-      if (!on) continue;
-      const float ms = __fdiv_rn(sums[0], float(D));
-      const float r = rstd ? __ldg(rstd + row) : rsqrtf(ms + eps);
-      const float c2 = norm_c2(sums[1], r, ms, eps, D);
+    }
+    if constexpr (LEV) {
+      float lo, hi;
+      f2_get(sxx, lo, hi);
+      sums[0] = lo + hi;
+      f2_get(sxa, lo, hi);
+      sums[1] = lo + hi;
+    }
+    group_sum<2>(sums, rg, red, flip);
+    if (threadIdx.x == 0 && !ahead.done(parts)) {   // the slot of the batch before this one takes the batch stages - 1 ahead
+      const int prev = s == 0 ? stages - 1 : s - 1;
+      // (the first time round that slot is fresh: a wait for parity 1 on a new barrier returns at once)
+      mbar_wait(ring.empty + 8u * prev, s == 0 ? phase ^ 1u : phase, abort_flag, status, kErrProducerWait);
+      fetch(prev, ahead);
+      ahead.next(rg.groups, T, parts);
+    }
+    if (on) {
+      const float ms = div_n(sums[0], D, inv_n);
+      const float r = rstd ? r_in : rsqrtf(ms + eps);
+      const float c2 = norm_c2(sums[1], r, ms, eps, D, inv_n);
+      const F2 rr = f2(r, r), cc = f2(c2, c2);
 #pragma unroll
       for (int i = 0; i < PP; ++i) {
         const int pc = rg.tg + i * rg.G;
         if (pc < pieces) {
-          float xf[8], dyf[8], g[8], d[8];
-          unpack8(xq[i], xf);
-          unpack8(dq[i], dyf);
-          unpack8(gq[i], g);
+          const uint4 dqi = piece(0, i), xqi = piece(1, i);
+          if constexpr (LEV) {
+            const uint4 rqi = dres ? piece(2, i) : make_uint4(0u, 0u, 0u, 0u);
+            uint32_t o[4];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            d[e] = norm_dx<LEV>(norm_a<LEV>(g[e], dyf[e]), r, c2, xf[e]);
-            dg[i][e] += norm_gc<LEV>(dyf[e], xf[e], r);
-          }
-          if (dres) {
-            float q[8];
-            unpack8(rq[i], q);
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t dw = word_of(dqi, q);
+              const F2 xx = f2_of(word_of(xqi, q)), aa = f2_of(mul_bf16x2(word_of(gq[i], q), dw));
+              dg[i][q] = f2_add(dg[i][q], f2_of(mul_bf16x2(dw, bf16x2_of(f2_mul(xx, rr)))));
+              o[q] = bf16x2_of(f2_add(f2_mul(aa, rr), f2_mul(cc, xx)));
+              if (dres) o[q] = bf16x2_of(f2_add(f2_of(word_of(rqi, q)), f2_of(o[q])));
+            }
+            *reinterpret_cast<uint4*>(dx + off + pc * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+          } else {
+            float xf[8], dyf[8], g[8], d[8], gc[8];
+            unpack8(xqi, xf);
+            unpack8(dqi, dyf);
+            unpack8(gq[i], g);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) d[e] = LEV ? __fadd_rn(q[e], rb(d[e])) : q[e] + d[e];
+            for (int e = 0; e < 8; ++e) {
+              d[e] = norm_dx<LEV>(norm_a<LEV>(g[e], dyf[e]), r, c2, xf[e]);
+              gc[e] = norm_gc<LEV>(dyf[e], xf[e], r);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dg[i][q] = f2_add(dg[i][q], f2(gc[2 * q], gc[2 * q + 1]));
+            if (dres) {
+              float q[8];
+              unpack8(piece(2, i), q);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) d[e] = q[e] + d[e];
+            }
+            *reinterpret_cast<uint4*>(dx + off + pc * 8) = pack8(d);
           }
-          *reinterpret_cast<uint4*>(dx + off + pc * 8) = pack8(d);
         }
       }
     }
-    if (partial) write_gain_partial<PP>(dg, rg, pieces, gsm, partial + p * D);
+    __syncwarp();   // the warp has read all it needs of the slot
+    if ((threadIdx.x & 31) == 0) mbar_arrive(ring.empty + 8u * s);
+    if (++s == stages) s = 0, phase ^= 1u;
+    if (w.last_of_part(rg.groups)) {
+      if (partial) write_gain_partial<PP>(dg, rg, pieces, gsm, partial + int64_t(w.part) * D);
+#pragma unroll
+      for (int i = 0; i < PP; ++i)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) dg[i][q] = f2(0.f, 0.f);
+    }
   }
+  if (threadIdx.x == 0 && *abort_flag) __nanosleep(200000);   // an expired wait: let copies in flight land first
 }
 
 }  // namespace
@@ -166,14 +250,22 @@ void rmsnorm_bwd_add(const bf16_t* dy, const bf16_t* x, const bf16_t* gain, cons
   const int pieces = D / 8;
   const int pp = pieces <= kGroupThreads ? 1 : pieces <= 2 * kGroupThreads ? 2 : 4;
   const int G = group_threads_for(pieces, pp);
+  const int ctas = pp == 1 ? 4 : pp == 2 ? 2 : 1;   // CTAs per SM the ring is sized for
+  const int nops = dres ? 3 : 2;
+  const uint32_t op_bytes = ring_op_bytes(kGroupThreads / G, D);
+  const int stages = ring_stages_for(ctas, nops, op_bytes, 4608);
+  const uint32_t smem = ring_bytes(stages, nops, op_bytes);
   auto kern = pp == 1   ? (lev ? k_rmsnorm_bwd_add<true, 1> : k_rmsnorm_bwd_add<false, 1>)
               : pp == 2 ? (lev ? k_rmsnorm_bwd_add<true, 2> : k_rmsnorm_bwd_add<false, 2>)
                         : (lev ? k_rmsnorm_bwd_add<true, 4> : k_rmsnorm_bwd_add<false, 4>);
-  kern<<<int(parts), kGroupThreads, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(dy),
-                                            reinterpret_cast<const __nv_bfloat16*>(x),
-                                            reinterpret_cast<const __nv_bfloat16*>(gain), rstd,
-                                            reinterpret_cast<const __nv_bfloat16*>(dres),
-                                            reinterpret_cast<__nv_bfloat16*>(dx), dgain_partial, T, D, eps, parts, G);
+  NM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  const int grid = int(std::min<int64_t>(parts, int64_t(ce::sm_count()) * ctas));
+  kern<<<grid, kGroupThreads, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(dy),
+                                          reinterpret_cast<const __nv_bfloat16*>(x),
+                                          reinterpret_cast<const __nv_bfloat16*>(gain), rstd,
+                                          reinterpret_cast<const __nv_bfloat16*>(dres),
+                                          reinterpret_cast<__nv_bfloat16*>(dx), dgain_partial, T, D, eps, parts, G, stages,
+                                          op_bytes, inv_if_pow2(D), row_status_word());
   NM_CUDA(cudaGetLastError());
 }
 
