@@ -577,8 +577,8 @@ def adjacent_kernels(env, tokens=65536, hidden=2048):
           lambda: lib.nm_sandwich_tail_fwd(1, 0, p(b), p(x), p(gain), p(gain), p(y), p(y2), p(rstd), p(rstd2), T, D,
                                            1e-5, None))
     timed("sandwich_tail_bwd", 6 * TD2,
-          lambda: lib.nm_sandwich_tail_bwd(1, 0, p(dy), p(dy2), p(y), p(gain), p(rstd2), p(b), p(gain), p(rstd), p(y3),
-                                           p(y2), None, None, T, D, 1e-5, None))
+          lambda: lib.nm_sandwich_tail_bwd_partial(1, 0, p(dy), p(dy2), p(y), p(gain), p(rstd2), p(b), p(gain), p(rstd),
+                                                   p(y3), p(y2), p(part), p(part[P:]), T, D, 1e-5, None))
     V, Rr = 128256, 4096
     store = torch.randn(Rr, V, generator=g, device="cuda").to(bf)
     lse = torch.full((Rr,), 12.0, device="cuda")

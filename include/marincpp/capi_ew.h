@@ -20,6 +20,13 @@ int nm_rmsnorm_bwd_add_partial(int dtype, int rounding, const void* dy, const vo
                                const float* rstd, const void* dres, void* dx, float* dgain_partial, int64_t T, int D,
                                float eps, void* stream);
 
+/* The sandwich tail backward with raw gain-gradient partials ([nm_norm_partial_rows(T), D] f32 each, nullptr: skipped),
+ * as the trainer calls it with buffers of its memory plan; nm_sandwich_tail_bwd (capi.h) is the same kernel followed by
+ * the fixed-order reduction of the partials. */
+int nm_sandwich_tail_bwd_partial(int dtype, int rounding, const void* dx_out, const void* da_next, const void* x_out,
+                                 const void* g_next, const float* rstd_next, const void* branch, const void* g_post,
+                                 const float* rstd_post, void* dx_in, void* dbranch, float* pg_next, float* pg_post,
+                                 int64_t T, int D, float eps, void* stream);
 /* The norm backward kernels (nm_rmsnorm_bwd_add, nm_rmsnorm_bwd_add_partial, nm_sandwich_tail_bwd) stage their operands
  * through a ring in shared memory whose waits are bounded; one that ran out leaves a bit in a per-GPU word built into the
  * library. This reads the word after the stream's work (it synchronises the stream), clears it when set, and returns

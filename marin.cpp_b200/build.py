@@ -20,6 +20,8 @@ SOURCES = ["nm_core.cpp", "ce_api.cpp", "capi_ce.cpp", "comm.cpp", "ce_gemm.cu",
            "ce_static_ws.cu", "ew_sandwich.cu", "ew_misc.cu", "opt_adamh.cu", "opt_api.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+# The norm kernels restate rounding points one IEEE operation at a time: no multiply-add contraction in their units.
+PER_SOURCE = {"ew_rmsnorm.cu": ["--fmad=false"], "ew_sandwich.cu": ["--fmad=false"]}
 COMMON = ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-Wall",
           "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
@@ -30,6 +32,7 @@ def _sources():
 
 def _fingerprint():
     h = hashlib.sha256()
+    h.update(open(os.path.abspath(__file__), "rb").read())
     for dirpath in (CSRC, os.path.join(ROOT, "include", "marincpp"), os.path.join(ROOT, "include", "marincpp", "kernels")):
         for name in sorted(os.listdir(dirpath)):
             path = os.path.join(dirpath, name)
@@ -56,6 +59,7 @@ def build(force=False, verbose=False):
             cmd += ["-Xptxas", "-v"] if verbose else []
         else:
             cmd = [NVCC] + ARCH + COMMON + ["-DNM_BUILD_ID=\"%s\"" % build_id]
+        cmd += PER_SOURCE.get(src, [])
         cmd += ["-c", src, "-o", obj]           # relative source name: __FILE__ in messages is the bare file name
         r = subprocess.run(cmd, capture_output=True, text=True, cwd=CSRC)
         if r.returncode != 0:

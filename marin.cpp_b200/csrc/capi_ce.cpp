@@ -316,7 +316,8 @@ int nm_sandwich_tail_bwd(int dtype, int rounding, const void* dx_out, const void
     const nm::Rounding r = rounding_of(rounding);
     const int64_t rows = nm::ew::norm_partial_rows(T);
     float* part = nullptr;   // test path: two partial buffers in one stream-ordered allocation
-    NM_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&part), size_t(rows) * D * 4 * 2, S(stream)));
+    const bool want_partials = dg_next || (dg_post && g_post);
+    if (want_partials) NM_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&part), size_t(rows) * D * 4 * 2, S(stream)));
     float* pn = part;
     float* pp = part + size_t(rows) * D;
     auto B = [](const void* p) { return static_cast<const nm::bf16_t*>(p); };
@@ -326,7 +327,19 @@ int nm_sandwich_tail_bwd(int dtype, int rounding, const void* dx_out, const void
     const bool rbf = r == nm::Rounding::Levanter;
     if (dg_next) nm::ew::reduce_partials_rows(pn, int(rows), D, dg_next, false, rbf, S(stream));
     if (dg_post && g_post) nm::ew::reduce_partials_rows(pp, int(rows), D, dg_post, false, rbf, S(stream));
-    NM_CUDA(cudaFreeAsync(part, S(stream)));
+    if (want_partials) NM_CUDA(cudaFreeAsync(part, S(stream)));
+  });
+}
+int nm_sandwich_tail_bwd_partial(int dtype, int rounding, const void* dx_out, const void* da_next, const void* x_out,
+                                 const void* g_next, const float* rstd_next, const void* branch, const void* g_post,
+                                 const float* rstd_post, void* dx_in, void* dbranch, float* pg_next, float* pg_post,
+                                 int64_t T, int D, float eps, void* stream) {
+  return guarded([&] {
+    NM_REQUIRE(dtype == 1, "nm_sandwich_tail_bwd_partial: bf16 storage (dtype 1) only");
+    auto B = [](const void* p) { return static_cast<const nm::bf16_t*>(p); };
+    nm::ew::sandwich_tail_bwd(B(dx_out), B(da_next), B(x_out), B(g_next), rstd_next, B(branch), B(g_post), rstd_post,
+                              static_cast<nm::bf16_t*>(dx_in), static_cast<nm::bf16_t*>(dbranch), pg_next, pg_post, T, D,
+                              eps, S(stream), rounding_of(rounding));
   });
 }
 int nm_doc_meta(const int32_t* tokens, const uint8_t* row_valid, int rows, int S_, int32_t eos, int max_segs,

@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) k_rmsnorm_fwd(const __nv_bfloa
 // registers, the group reduces sum x^2 and sum x a, and the same registers feed the output pass. Gain-gradient sums stay
 // in the owning thread's registers for the whole part.
 template <bool LEV, int PP>
-__global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_rmsnorm_bwd_add(const __nv_bfloat16* dy,
+__global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : PP == 2 ? 2 : 1) k_rmsnorm_bwd_add(const __nv_bfloat16* dy,
                                                                 const __nv_bfloat16* x,
                                                                 const __nv_bfloat16* __restrict__ gain,
                                                                 const float* __restrict__ rstd,
@@ -177,8 +177,8 @@ __global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_rmsnorm_bwd_
               const uint32_t dw = word_of(dqi, q);
               const F2 xx = f2_of(word_of(xqi, q)), aa = f2_of(mul_bf16x2(word_of(gq[i], q), dw));
               dg[i][q] = f2_add(dg[i][q], f2_of(mul_bf16x2(dw, bf16x2_of(f2_mul(xx, rr)))));
-              o[q] = bf16x2_of(f2_add(f2_mul(aa, rr), f2_mul(cc, xx)));
-              if (dres) o[q] = bf16x2_of(f2_add(f2_of(word_of(rqi, q)), f2_of(o[q])));
+              o[q] = axpby_bf16x2(aa, rr, cc, xx);
+              if (dres) o[q] = add_bf16x2(word_of(rqi, q), o[q]);
             }
             *reinterpret_cast<uint4*>(dx + off + pc * 8) = make_uint4(o[0], o[1], o[2], o[3]);
           } else {
@@ -248,7 +248,7 @@ void rmsnorm_bwd_add(const bf16_t* dy, const bf16_t* x, const bf16_t* gain, cons
   const int64_t parts = norm_partial_rows(T);
   const bool lev = r == Rounding::Levanter;
   const int pieces = D / 8;
-  const int pp = pieces <= kGroupThreads ? 1 : pieces <= 2 * kGroupThreads ? 2 : 4;
+  const int pp = pieces_per_thread_for(pieces);
   const int G = group_threads_for(pieces, pp);
   const int ctas = pp == 1 ? 4 : pp == 2 ? 2 : 1;   // CTAs per SM the ring is sized for
   const int nops = dres ? 3 : 2;

@@ -72,6 +72,10 @@ struct RowGroup {
 __device__ __forceinline__ RowGroup row_group(int G) {
   return RowGroup{G, int(threadIdx.x) / G, int(threadIdx.x) % G, kGroupThreads / G};
 }
+// Host: PP of the backward kernels for a row of `pieces` pieces. Two pieces per thread wherever a row fills a warp
+// that way: the work per row that does not depend on its length (sums, statistics, waits, index arithmetic) is then
+// spread over 16 elements instead of 8, and it is that work, not HBM, which bounds these kernels at one piece per thread.
+inline int pieces_per_thread_for(int pieces) { return pieces <= 32 ? 1 : pieces <= 2 * kGroupThreads ? 2 : 4; }
 inline int group_threads_for(int pieces, int pp) {   // host: smallest G with G * pp >= pieces
   for (int g = 32; g < kGroupThreads; g *= 2)
     if (g * pp >= pieces) return g;
@@ -154,6 +158,11 @@ __device__ __forceinline__ F2 f2_add(F2 a, F2 b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
   return r;
 }
+// bf16x2(a r + c x) with three roundings per element before the bf16 one (two products, one sum). The sum is taken with
+// scalar add.rn.f32: ptxas was seen to merge a mul.rn.f32x2 feeding an add.rn.f32x2 into one fma (a single rounding, which
+// shows as a different bf16 result where the sum lands next to a tie), with or without --fmad=false; a scalar add with an
+// explicit rounding mode is never contracted.
+__device__ __forceinline__ uint32_t axpby_bf16x2(F2 a, F2 r, F2 c, F2 x);
 __device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) {
   F2 r;
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v));
@@ -187,6 +196,14 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
+// bf16(f32(a) + f32(b)) for two elements: the f32 sum of two bf16 values rounded again to bf16 equals the exact sum
+// rounded once (24 bits are more than twice 8 plus 2, so the first rounding cannot move the second), which is what
+// add.rn.bf16x2 returns.
+__device__ __forceinline__ uint32_t add_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -198,6 +215,12 @@ __device__ __forceinline__ uint32_t bf16x2_of(F2 a) {   // both halves rounded t
   float lo, hi;
   f2_get(a, lo, hi);
   return pack_bf16x2(lo, hi);
+}
+__device__ __forceinline__ uint32_t axpby_bf16x2(F2 a, F2 r, F2 c, F2 x) {
+  float p0, p1, q0, q1;
+  f2_get(f2_mul(a, r), p0, p1);
+  f2_get(f2_mul(c, x), q0, q1);
+  return pack_bf16x2(__fadd_rn(p0, q0), __fadd_rn(p1, q1));
 }
 __device__ __forceinline__ uint32_t word_of(const uint4& q, int i) { return i == 0 ? q.x : i == 1 ? q.y : i == 2 ? q.z : q.w; }
 

@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) k_sandwich_fwd(const __nv_bflo
 // and stored, the group reduces sum branch a_post, and the branch gradient follows from the registers that are still
 // there. Gain-gradient sums of both norms stay in the owning thread's registers for the whole part.
 template <bool LEV, int PP>
-__global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_sandwich_bwd(const __nv_bfloat16* dx_out,
+__global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : PP == 2 ? 2 : 1) k_sandwich_bwd(const __nv_bfloat16* dx_out,
                                                              const __nv_bfloat16* da_next,
                                                              const __nv_bfloat16* x_out,
                                                              const __nv_bfloat16* __restrict__ g_next,
@@ -237,8 +237,8 @@ __global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_sandwich_bwd
             const uint32_t dw = word_of(aqi, q);
             const F2 xx = f2_of(word_of(xqi, q)), aa = f2_of(mul_bf16x2(word_of(gnq[i], q), dw));
             dgn[i][q] = f2_add(dgn[i][q], f2_of(mul_bf16x2(dw, bf16x2_of(f2_mul(xx, rrn)))));
-            const uint32_t nw = bf16x2_of(f2_add(f2_mul(aa, rrn), f2_mul(ccn, xx)));
-            m[q] = bf16x2_of(f2_add(f2_of(word_of(oqi, q)), f2_of(nw)));
+            const uint32_t nw = axpby_bf16x2(aa, rrn, ccn, xx);
+            m[q] = add_bf16x2(word_of(oqi, q), nw);
           }
           mq[i] = make_uint4(m[0], m[1], m[2], m[3]);
         } else {
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(kGroupThreads, PP == 1 ? 4 : 1) k_sandwich_bwd
                 const uint32_t mw = word_of(mq[i], q);
                 const F2 bb = f2_of(word_of(bqi, q)), ap = f2_of(mul_bf16x2(word_of(gpq[i], q), mw));
                 dgp[i][q] = f2_add(dgp[i][q], f2_of(mul_bf16x2(mw, bf16x2_of(f2_mul(bb, rrp)))));
-                o[q] = bf16x2_of(f2_add(f2_mul(ap, rrp), f2_mul(ccp, bb)));
+                o[q] = axpby_bf16x2(ap, rrp, ccp, bb);
               }
               *reinterpret_cast<uint4*>(dbranch + off + pc * 8) = make_uint4(o[0], o[1], o[2], o[3]);
             } else {
@@ -375,7 +375,7 @@ void sandwich_tail_bwd(const bf16_t* dx_out, const bf16_t* da_next, const bf16_t
   const int64_t parts = norm_partial_rows(T);
   const bool lev = r == Rounding::Levanter;
   const int pieces = D / 8;
-  const int pp = pieces <= kGroupThreads ? 1 : pieces <= 2 * kGroupThreads ? 2 : 4;
+  const int pp = pieces_per_thread_for(pieces);
   const int G = group_threads_for(pieces, pp);
   const int ctas = pp == 1 ? 4 : pp == 2 ? 2 : 1;   // CTAs per SM the ring is sized for
   const int nops = g_post ? 4 : 3;

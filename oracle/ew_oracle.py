@@ -50,3 +50,65 @@ def sum_fixed(x):
         s[:o] = (s[:o] + s[o:2 * o]).astype(np.float32)
         o >>= 1
     return np.float32(s[0])
+
+
+# ----------------------------------------------------------------------------------------------- norm backward (levanter)
+# Restates the rounding points of the reference's levanter instantiations (src/kernels/elementwise/rmsnorm_kernels.cuh:3-10,
+# k_rmsnorm_bwd_add :52-100, k_sandwich_bwd :170-235): every product and sum below is one IEEE f32 operation (numpy does
+# not contract), `bf` rounds to bf16 (nearest even) and widens again. Row sums are taken in float64 and rounded to f32
+# once: equal to an f32 sum in ANY order whenever all partial sums are exactly representable, which the parity tests
+# arrange by drawing the summed operands from small dyadic grids. The saved statistics r (rstd) are inputs, as in the
+# trainer's call; rsqrtf itself is not restated.
+def bf(a):
+    """float32 array -> float32 array holding the bf16 roundings (nearest, ties to even)."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    return r.view(np.float32).reshape(np.shape(a))
+
+
+def _c2(s, r, ms, eps, n):
+    f = np.float32
+    return f(2) * ((s * (f(-0.5) * (r / (ms + f(eps))))) / f(n))
+
+
+def _norm_bwd_rows(g, dy, x, r, eps):
+    """One norm's backward over rows: returns (dx before any residual add, as bf16-valued f32; gc = bf16(dy bf16(x r));
+    ms). g [D]; dy, x [T, D] bf16-valued f32; r [T] f32."""
+    f = np.float32
+    D = x.shape[1]
+    a = bf(g[None, :] * dy)
+    sxx = (x.astype(np.float64) ** 2).sum(1).astype(f)
+    sxa = (x.astype(np.float64) * a.astype(np.float64)).sum(1).astype(f)
+    ms = sxx / f(D)
+    c2 = _c2(sxa, r, ms, eps, D)
+    dx = bf(a * r[:, None] + c2[:, None] * x)
+    gc = bf(dy * bf(x * r[:, None]))
+    return dx, gc, ms
+
+
+def rmsnorm_bwd_add_levanter(dy, x, gain, rstd, dres, eps):
+    """-> (dx, gc): dx = bf16(a r + c2 x), with a residual gradient bf16(dres + dx); gc [T, D] are the per-row terms of
+    the gain gradient (the kernel sums them over the rows of a part in f32)."""
+    f = np.float32
+    dx, gc, _ = _norm_bwd_rows(np.asarray(gain, f), np.asarray(dy, f), np.asarray(x, f), np.asarray(rstd, f), eps)
+    if dres is not None:
+        dx = bf(np.asarray(dres, f) + dx)
+    return dx, gc
+
+
+def sandwich_bwd_levanter(dx_out, da_next, x_out, g_next, rstd_next, branch, g_post, rstd_post, eps):
+    """-> (dx_in, dbranch, gc_next, gc_post, sba): dx_mid = bf16(dx_out + norm_next_bwd(da_next)); dx_in = dx_mid; with a
+    post-norm dbranch = norm_post_bwd(dx_mid) over the branch output, else dbranch = dx_mid. sba [T] is the post-norm's
+    row sum of branch * a_post in float64 (its summands are not on a dyadic grid: callers compare dbranch with a
+    tolerance of one bf16 step on a small fraction of elements)."""
+    f = np.float32
+    dxn, gcn, _ = _norm_bwd_rows(np.asarray(g_next, f), np.asarray(da_next, f), np.asarray(x_out, f),
+                                 np.asarray(rstd_next, f), eps)
+    dxm = bf(np.asarray(dx_out, f) + dxn)
+    if g_post is None:
+        return dxm, dxm, gcn, None, None
+    b = np.asarray(branch, f)
+    db, gcp, _ = _norm_bwd_rows(np.asarray(g_post, f), dxm, b, np.asarray(rstd_post, f), eps)
+    ap = bf(np.asarray(g_post, f)[None, :] * dxm)
+    sba = (b.astype(np.float64) * ap.astype(np.float64)).sum(1)
+    return dxm, db, gcn, gcp, sba

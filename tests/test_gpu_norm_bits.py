@@ -1,0 +1,116 @@
+"""Bit parity of the norm backward kernels (levanter rounding) with the numpy restatement of the reference's rounding
+points (oracle/ew_oracle.py). The operands that enter the row sums are drawn from small dyadic grids, so that every
+partial sum is exact in f32 and the sums do not depend on the order of addition; everything else (the saved statistics,
+the residual gradients) is arbitrary. dx / dx_in must then match bit for bit; the gain-gradient partials are sums of
+per-row bf16 terms over the rows of a part (f32, order fixed by the kernel's geometry) and are compared with the float64
+sum of the oracle's terms; the post-norm branch gradient depends on a row sum whose summands are not on a grid and is
+allowed one bf16 step on a small fraction of elements. Also: the status word of the kernels' bounded waits stays 0."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+EPS = 1e-5
+
+
+def _grid(rng, shape, steps, scale):
+    """bf16-exact values k * scale, k in [-steps, steps]"""
+    return (rng.integers(-steps, steps + 1, size=shape).astype(np.float32) * np.float32(scale))
+
+
+def _dev(a, dtype=torch.bfloat16):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda().to(dtype)
+
+
+def _bits(t):
+    return t.view(torch.int16).cpu().numpy()
+
+
+def _bits_of(a):
+    return (np.ascontiguousarray(a, np.float32).view(np.uint32) >> 16).astype(np.uint16).view(np.int16)
+
+
+def _part_sums(gc, parts):
+    T = gc.shape[0]
+    return np.stack([gc[p * T // parts:(p + 1) * T // parts].sum(0, dtype=np.float64) for p in range(parts)])
+
+
+def _status_is_zero(L):
+    word = ctypes.c_uint32(77)
+    assert L.nm_norm_bwd_device_status(None, ctypes.byref(word)) == 0 and word.value == 0
+
+
+@pytest.mark.parametrize("T,D", [(777, 2048), (300, 512), (1500, 1024), (129, 136), (64, 256), (210, 4096), (97, 8192),
+                                 (40, 4104)])
+@pytest.mark.parametrize("with_res", [True, False])
+def test_rmsnorm_bwd_bits(T, D, with_res):
+    from gpu_common import lib, nmce
+    import ew_oracle
+    rng = np.random.default_rng(T + D)
+    x = _grid(rng, (T, D), 8, 0.25)
+    dy = _grid(rng, (T, D), 8, 2.0 ** -10)
+    gain = _grid(rng, (D,), 2, 0.5) + np.float32(1.5)          # 0.5 .. 2.5 in steps of 0.5
+    rstd = (1.0 / np.sqrt((x.astype(np.float64) ** 2).mean(1) + EPS) * rng.uniform(0.9, 1.1, T)).astype(np.float32)
+    dres = ew_oracle.bf(rng.standard_normal((T, D)).astype(np.float32) * 1e-2) if with_res else None
+    want_dx, gc = ew_oracle.rmsnorm_bwd_add_levanter(dy, x, gain, rstd, dres, EPS)
+    L = lib()
+    P = int(L.nm_norm_partial_rows(T))
+    dx = torch.empty(T, D, dtype=torch.bfloat16, device="cuda")
+    part = torch.full((P, D), float("nan"), device="cuda")
+    d_dy, d_x, d_g, d_r = _dev(dy), _dev(x), _dev(gain), _dev(rstd, torch.float32)
+    d_res = _dev(dres) if with_res else None
+    L.nm_rmsnorm_bwd_add_partial(1, 0, nmce.ptr(d_dy), nmce.ptr(d_x), nmce.ptr(d_g), nmce.ptr(d_r), nmce.ptr(d_res),
+                                 nmce.ptr(dx), nmce.ptr(part), T, D, EPS, None)
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(dx), _bits_of(want_dx))
+    np.testing.assert_allclose(part.cpu().numpy(), _part_sums(gc, P), rtol=2e-5, atol=1e-7)
+    if with_res:   # in place over the residual gradient: same bits
+        L.nm_rmsnorm_bwd_add_partial(1, 0, nmce.ptr(d_dy), nmce.ptr(d_x), nmce.ptr(d_g), nmce.ptr(d_r), nmce.ptr(d_res),
+                                     nmce.ptr(d_res), None, T, D, EPS, None)
+        torch.cuda.synchronize()
+        assert np.array_equal(_bits(d_res), _bits_of(want_dx))
+    _status_is_zero(L)
+
+
+@pytest.mark.parametrize("T,D", [(777, 2048), (300, 512), (1500, 1024), (129, 136), (64, 256), (210, 4096), (97, 8192)])
+@pytest.mark.parametrize("post", [True, False])
+def test_sandwich_bwd_bits(T, D, post):
+    from gpu_common import lib, nmce
+    import ew_oracle
+    rng = np.random.default_rng(3 * T + D + int(post))
+    xo = _grid(rng, (T, D), 8, 0.25)
+    b = _grid(rng, (T, D), 8, 0.25)
+    da = _grid(rng, (T, D), 8, 2.0 ** -10)
+    gn = _grid(rng, (D,), 2, 0.5) + np.float32(1.5)
+    gp = ew_oracle.bf((1 + 0.2 * rng.standard_normal(D)).astype(np.float32)) if post else None
+    dxo = ew_oracle.bf(rng.standard_normal((T, D)).astype(np.float32) * 1e-2)
+    rn = (1.0 / np.sqrt((xo.astype(np.float64) ** 2).mean(1) + EPS) * rng.uniform(0.9, 1.1, T)).astype(np.float32)
+    rp = (1.0 / np.sqrt((b.astype(np.float64) ** 2).mean(1) + EPS) * rng.uniform(0.9, 1.1, T)).astype(np.float32)
+    want_in, want_br, gcn, gcp, _ = ew_oracle.sandwich_bwd_levanter(dxo, da, xo, gn, rn, b if post else None, gp,
+                                                                    rp if post else None, EPS)
+    L = lib()
+    P = int(L.nm_norm_partial_rows(T))
+    dx_in = torch.empty(T, D, dtype=torch.bfloat16, device="cuda")
+    dbr = torch.empty(T, D, dtype=torch.bfloat16, device="cuda")
+    pgn = torch.full((P, D), float("nan"), device="cuda")
+    pgp = torch.full((P, D), float("nan"), device="cuda")
+    d = dict(dxo=_dev(dxo), da=_dev(da), xo=_dev(xo), gn=_dev(gn), rn=_dev(rn, torch.float32), b=_dev(b),
+             gp=_dev(gp) if post else None, rp=_dev(rp, torch.float32) if post else None)
+    p = nmce.ptr
+    L.nm_sandwich_tail_bwd_partial(1, 0, p(d["dxo"]), p(d["da"]), p(d["xo"]), p(d["gn"]), p(d["rn"]), p(d["b"]),
+                                   p(d["gp"]), p(d["rp"]), p(dx_in), p(dbr), p(pgn), p(pgp) if post else None, T, D,
+                                   EPS, None)
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(dx_in), _bits_of(want_in))
+    np.testing.assert_allclose(pgn.cpu().numpy(), _part_sums(gcn, P), rtol=2e-5, atol=1e-7)
+    if post:
+        got, want = _bits(dbr).astype(np.int32), _bits_of(want_br).astype(np.int32)
+        off = got != want
+        assert off.mean() < 5e-3 and (np.abs(got - want)[off] <= 1).all()
+        # the gain terms of the post-norm are functions of dx_mid, the branch and the saved statistic only: exact terms
+        np.testing.assert_allclose(pgp.cpu().numpy(), _part_sums(gcp, P), rtol=2e-5, atol=1e-7)
+    else:
+        assert np.array_equal(_bits(dbr), _bits_of(want_in))
+    _status_is_zero(L)
