@@ -1,6 +1,6 @@
 // RMSNorm forward and backward (+ residual add, + gain-gradient partials) in bf16 storage, for the readout head.
-// One warp per row; a lane owns the 16-byte pieces lane, lane + 32, ... of the row, so a row of D <= 8192 stays in
-// registers between the reduction and the output pass.
+// Forward: one warp per row, a lane owning the 16-byte pieces lane, lane + 32, ... of it. Backward: row groups over a ring
+// of row batches in shared memory (ew_rows.cuh), rows of D <= 8192.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -13,36 +13,114 @@
 namespace nm::ew {
 namespace {
 
-template <bool LEV>
-__global__ void __launch_bounds__(kRowWarps * 32) k_rmsnorm_fwd(const __nv_bfloat16* __restrict__ x,
-                                                             const __nv_bfloat16* __restrict__ gain,
-                                                             __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
-                                                             int64_t T, int D, float eps) {
-  const int lane = threadIdx.x & 31;
+// Forward: a CTA walks parts of consecutive rows in batches, row groups and batch ring as described in ew_rows.cuh. A
+// thread reads its pieces of x from the landed batch for the sum of squares and again for the output.
+template <bool LEV, int PP>
+__global__ void __launch_bounds__(kGroupThreads, PP <= 2 ? 2 : 1) k_rmsnorm_fwd(const __nv_bfloat16* x,
+                                                                               const __nv_bfloat16* __restrict__ gain,
+                                                                               __nv_bfloat16* y, float* __restrict__ rstd,
+                                                                               int64_t T, int D, float eps, int64_t parts,
+                                                                               int G, int stages, uint32_t op_bytes,
+                                                                               float inv_n, uint32_t* status) {
+  using namespace nm::ptx;
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  __shared__ __align__(16) float red[2 * 8];
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  const RowGroup rg = row_group(G);
   const int pieces = D / 8;
-  for (int64_t row = blockIdx.x * int64_t(kRowWarps) + (threadIdx.x >> 5); row < T; row += int64_t(gridDim.x) * kRowWarps) {
-    const __nv_bfloat16* xr = x + row * D;
-    float ss = 0.f;
-    for (int pc = lane; pc < pieces; pc += 32) {
-      float f[8];
-      load8(xr + pc * 8, f);
+  RowRing ring;
+  ring.data = (smem_u32(ring_raw) + 127u) & ~127u;
+  ring.op_bytes = op_bytes, ring.stages = stages, ring.nops = 1;
+  ring.full = ring.data + uint32_t(stages) * op_bytes;
+  ring.empty = ring.full + 8u * stages;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(ring.full + 8u * s, 1), mbar_init(ring.empty + 8u * s, kRingWarps);
+    abort_word = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  auto fetch = [&](int s, const BatchWalk& b) {   // thread 0: one batch into slot s
+    const uint32_t bytes = b.rows(rg.groups) * uint32_t(D) * 2u;
+    const uint32_t bar = ring.full + 8u * s;
+    mbar_arrive_expect_tx(bar, bytes);
+    bulk_load(ring.slot(s, 0), x + b.row * D, bytes, bar);
+  };
+  BatchWalk w, ahead;
+  w.begin(T, parts);
+  ahead = w;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages - 1 && !ahead.done(parts); ++s, ahead.next(rg.groups, T, parts)) fetch(s, ahead);
+  }
+  int flip = 0;
+  uint4 gq[PP];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
-    }
-    ss = warp_sum(ss);
-    const float r = rsqrtf(__fdiv_rn(ss, float(D)) + eps);
-    if (rstd && lane == 0) rstd[row] = r;
-    if (y) {
-      for (int pc = lane; pc < pieces; pc += 32) {
-        float f[8], g[8], o[8];
-        load8(xr + pc * 8, f);
-        load8(gain + pc * 8, g);
+  for (int i = 0; i < PP; ++i) {
+    const int pc = rg.tg + i * rg.G;
+    gq[i] = (y && pc < pieces) ? ldg16(gain + pc * 8) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  int s = 0;
+  uint32_t phase = 0;
+  for (; !w.done(parts); w.next(rg.groups, T, parts)) {
+    const int64_t row = w.row + rg.group;
+    const bool on = row < w.end;
+    const int64_t off = row * D;
+    mbar_wait<true>(ring.full + 8u * s, phase, abort_flag, status, kErrTransformWait);
+    const uint32_t at0 = ring.slot(s, 0) + uint32_t(rg.group * D + rg.tg * 8) * 2u;
+    auto piece = [&](int i) {
+      const int pc = rg.tg + i * rg.G;
+      return (on && pc < pieces) ? ld_shared_v4(at0 + uint32_t(i * rg.G) * 16u) : make_uint4(0u, 0u, 0u, 0u);
+    };
+    F2 sxx = f2(0.f, 0.f);   // even and odd elements summed apart, two per instruction (the squares are exact in f32)
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = LEV ? __fmul_rn(g[e], rb(__fmul_rn(f[e], r))) : g[e] * (f[e] * r);
-        store8(y + row * D + pc * 8, o);
+    for (int i = 0; i < PP; ++i) {
+      const uint4 xqi = piece(i);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const F2 xx = f2_of(word_of(xqi, q));
+        sxx = f2_fma(xx, xx, sxx);
       }
     }
+    float sums[1];
+    {
+      float lo, hi;
+      f2_get(sxx, lo, hi);
+      sums[0] = lo + hi;
+    }
+    group_sum<1>(sums, rg, red, flip);
+    if (threadIdx.x == 0 && !ahead.done(parts)) {   // the slot of the batch before this one takes the batch stages - 1 ahead
+      const int prev = s == 0 ? stages - 1 : s - 1;
+      mbar_wait(ring.empty + 8u * prev, s == 0 ? phase ^ 1u : phase, abort_flag, status, kErrProducerWait);
+      fetch(prev, ahead);
+      ahead.next(rg.groups, T, parts);
+    }
+    if (on) {
+      const float r = rsqrtf(div_n(sums[0], D, inv_n) + eps);
+      if (rstd && rg.tg == 0) rstd[row] = r;
+      if (y) {
+        const F2 rr = f2(r, r);
+#pragma unroll
+        for (int i = 0; i < PP; ++i) {
+          const int pc = rg.tg + i * rg.G;
+          if (pc < pieces) {
+            const uint4 xqi = piece(i);
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const F2 xr = f2_mul(f2_of(word_of(xqi, q)), rr);
+              if constexpr (LEV) o[q] = mul_bf16x2(word_of(gq[i], q), bf16x2_of(xr));   // bf16(g bf16(x r))
+              else o[q] = bf16x2_of(f2_mul(f2_of(word_of(gq[i], q)), xr));
+            }
+            *reinterpret_cast<uint4*>(y + off + pc * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+      }
+    }
+    __syncwarp();   // the warp has read all it needs of the slot
+    if ((threadIdx.x & 31) == 0) mbar_arrive(ring.empty + 8u * s);
+    if (++s == stages) s = 0, phase ^= 1u;
   }
+  if (threadIdx.x == 0 && *abort_flag) __nanosleep(200000);   // an expired wait: let copies in flight land first
 }
 
 // A CTA walks parts of consecutive rows (the partition of norm_partial_rows) in batches, row groups and batch ring as
@@ -229,13 +307,26 @@ void rmsnorm_fwd(const bf16_t* x, const bf16_t* gain, bf16_t* y, float* rstd, in
                  cudaStream_t st, Rounding r) {
   NM_REQUIRE(x && gain && T >= 0 && D > 0 && D % 8 == 0, "rmsnorm_fwd: x, gain, D % 8 == 0");
   NM_REQUIRE(aligned16(x, gain, y), "rmsnorm_fwd: x, gain, y must be 16-byte aligned");
+  NM_REQUIRE(D <= kGroupThreads * 4 * 8, "rmsnorm_fwd: D <= 8192");
   if (T == 0) return;
-  const int grid = int(std::min<int64_t>((T + kRowWarps - 1) / kRowWarps, int64_t(ce::sm_count()) * 8));
-  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
-  auto G = reinterpret_cast<const __nv_bfloat16*>(gain);
-  auto Y = reinterpret_cast<__nv_bfloat16*>(y);
-  if (r == Rounding::Levanter) k_rmsnorm_fwd<true><<<grid, kRowWarps * 32, 0, st>>>(X, G, Y, rstd, T, D, eps);
-  else k_rmsnorm_fwd<false><<<grid, kRowWarps * 32, 0, st>>>(X, G, Y, rstd, T, D, eps);
+  const bool lev = r == Rounding::Levanter;
+  const int pieces = D / 8;
+  const int pp = pieces_per_thread_for(pieces);
+  const int G = group_threads_for(pieces, pp);
+  const int ctas = pp <= 2 ? 2 : 1;
+  const int64_t parts = norm_partial_rows(T);   // any partition of the rows would do; this one divides evenly over the grid
+  const uint32_t op_bytes = ring_op_bytes(kGroupThreads / G, D);
+  const int stages = ring_stages_for(ctas, 1, op_bytes, 512, 6);
+  const uint32_t smem = ring_bytes(stages, 1, op_bytes);
+  auto kern = pp == 1   ? (lev ? k_rmsnorm_fwd<true, 1> : k_rmsnorm_fwd<false, 1>)
+              : pp == 2 ? (lev ? k_rmsnorm_fwd<true, 2> : k_rmsnorm_fwd<false, 2>)
+                        : (lev ? k_rmsnorm_fwd<true, 4> : k_rmsnorm_fwd<false, 4>);
+  NM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  const int grid = int(std::min<int64_t>(parts, int64_t(ce::sm_count()) * ctas));
+  kern<<<grid, kGroupThreads, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(x),
+                                          reinterpret_cast<const __nv_bfloat16*>(gain),
+                                          reinterpret_cast<__nv_bfloat16*>(y), rstd, T, D, eps, parts, G, stages, op_bytes,
+                                          inv_if_pow2(D), row_status_word());
   NM_CUDA(cudaGetLastError());
 }
 

@@ -1,5 +1,6 @@
-// Row helpers shared by the RMSNorm and sandwich-tail kernels (bf16 storage): one warp owns a row, a lane owns the
-// 16-byte pieces lane, lane + 32, ... of it.
+// Row helpers shared by the RMSNorm and sandwich-tail kernels (bf16 storage). Forward kernels: one warp owns a row, a lane
+// owns the 16-byte pieces lane, lane + 32, ... of it. Backward kernels: row groups fed by a ring of row batches in shared
+// memory, packed bf16x2 / f32x2 arithmetic for the levanter rounding points (all further down).
 #pragma once
 
 #include <cuda_bf16.h>
@@ -59,9 +60,8 @@ __device__ __forceinline__ float norm_y(float g, float x, float r) {
 
 // ------------------------------------------------------------------------------------------------ row groups
 // Geometry of the backward kernels: a CTA of 256 threads works on 256 / G rows at a time, G threads side by side on a
-// row (G = 32, 64, 128 or 256), thread tg owning the 16-byte pieces tg, tg + G, ... (PP of them). A thread therefore
-// keeps a whole row's share in a few registers between the reduction and the output pass (no second load), and owns
-// the same columns for every row, so its gain-gradient sums never leave its registers until the part is done.
+// row (G = 32, 64, 128 or 256), thread tg owning the 16-byte pieces tg, tg + G, ... (PP of them). A thread owns the same
+// columns for every row, so its gain-gradient sums never leave its registers until the part is done.
 constexpr int kGroupThreads = 256;
 struct RowGroup {
   int G;        // threads per row
@@ -299,10 +299,10 @@ inline __host__ __device__ uint32_t ring_bytes(int stages, int nops, uint32_t op
 }
 // Host: the slot size of an operand and the number of stages that fit when `ctas` CTAs share an SM.
 inline uint32_t ring_op_bytes(int groups, int D) { return (uint32_t(groups) * uint32_t(D) * 2u + 127u) & ~127u; }
-inline int ring_stages_for(int ctas, int nops, uint32_t op_bytes, uint32_t static_bytes) {
-  const int64_t budget = int64_t(227) * 1024 / ctas - 1024 - static_bytes - 16 * 4 - 128;
+inline int ring_stages_for(int ctas, int nops, uint32_t op_bytes, uint32_t static_bytes, int most = 4) {
+  const int64_t budget = int64_t(227) * 1024 / ctas - 1024 - static_bytes - 16 * most - 128;
   const int64_t fit = budget / (int64_t(nops) * op_bytes);
-  return int(fit < 2 ? 2 : fit > 4 ? 4 : fit);
+  return int(fit < 2 ? 2 : fit > most ? most : fit);
 }
 
 }  // namespace nm::ew

@@ -18,68 +18,160 @@
 namespace nm::ew {
 namespace {
 
-template <bool LEV>
-__global__ void __launch_bounds__(kRowWarps * 32) k_sandwich_fwd(const __nv_bfloat16* __restrict__ branch,
-                                                                 const __nv_bfloat16* __restrict__ x_in,
-                                                                 const __nv_bfloat16* __restrict__ g_post,
-                                                                 const __nv_bfloat16* __restrict__ g_next,
-                                                                 __nv_bfloat16* __restrict__ x_out,
-                                                                 __nv_bfloat16* __restrict__ a_next,
-                                                                 float* __restrict__ rstd_post,
-                                                                 float* __restrict__ rstd_next, int64_t T, int D,
-                                                                 float eps) {
-  const int lane = threadIdx.x & 31;
+// Forward: a CTA walks parts of consecutive rows in batches, row groups and batch ring as described in ew_rows.cuh. A
+// thread reads its pieces of the branch output and of x_in from the landed batch; x_out stays in its registers (as
+// stored, rounded) between the second row sum and the next norm's output.
+template <bool LEV, int PP>
+__global__ void __launch_bounds__(kGroupThreads, PP <= 2 ? 2 : 1) k_sandwich_fwd(const __nv_bfloat16* branch,
+                                                                                const __nv_bfloat16* x_in,
+                                                                                const __nv_bfloat16* __restrict__ g_post,
+                                                                                const __nv_bfloat16* __restrict__ g_next,
+                                                                                __nv_bfloat16* x_out, __nv_bfloat16* a_next,
+                                                                                float* __restrict__ rstd_post,
+                                                                                float* __restrict__ rstd_next, int64_t T,
+                                                                                int D, float eps, int64_t parts, int G,
+                                                                                int stages, uint32_t op_bytes, float inv_n,
+                                                                                uint32_t* status) {
+  using namespace nm::ptx;
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  __shared__ __align__(16) float red[2 * 8];
+  __shared__ __align__(16) float red1[2 * 8];
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  const RowGroup rg = row_group(G);
   const int pieces = D / 8;
-  for (int64_t row = blockIdx.x * int64_t(kRowWarps) + (threadIdx.x >> 5); row < T;
-       row += int64_t(gridDim.x) * kRowWarps) {
-    const int64_t off = row * D;
-    float r_p = 0.f;
-    if (g_post) {
-      float ss = 0.f;
-      for (int pc = lane; pc < pieces; pc += 32) {
-        float b[8];
-        load8(branch + off + pc * 8, b);
+  const bool post = g_post != nullptr;
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  RowRing ring;
+  ring.data = (smem_u32(ring_raw) + 127u) & ~127u;
+  ring.op_bytes = op_bytes, ring.stages = stages, ring.nops = 2;
+  ring.full = ring.data + uint32_t(stages * 2) * op_bytes;
+  ring.empty = ring.full + 8u * stages;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(ring.full + 8u * s, 1), mbar_init(ring.empty + 8u * s, kRingWarps);
+    abort_word = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  auto fetch = [&](int s, const BatchWalk& b) {   // thread 0: one batch of both operands into slot s
+    const uint32_t bytes = b.rows(rg.groups) * uint32_t(D) * 2u;
+    const uint32_t bar = ring.full + 8u * s;
+    mbar_arrive_expect_tx(bar, bytes * 2u);
+    bulk_load(ring.slot(s, 0), branch + b.row * D, bytes, bar);
+    bulk_load(ring.slot(s, 1), x_in + b.row * D, bytes, bar);
+  };
+  BatchWalk w, ahead;
+  w.begin(T, parts);
+  ahead = w;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages - 1 && !ahead.done(parts); ++s, ahead.next(rg.groups, T, parts)) fetch(s, ahead);
+  }
+  int flip = 0, flip1 = 0;
+  uint4 gnq[PP], gpq[PP];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) ss = fmaf(b[e], b[e], ss);
+  for (int i = 0; i < PP; ++i) {
+    const int pc = rg.tg + i * rg.G;
+    gnq[i] = (a_next && pc < pieces) ? ldg16(g_next + pc * 8) : zero4;
+    gpq[i] = (post && pc < pieces) ? ldg16(g_post + pc * 8) : zero4;
+  }
+  int s = 0;
+  uint32_t phase = 0;
+  for (; !w.done(parts); w.next(rg.groups, T, parts)) {
+    const int64_t row = w.row + rg.group;
+    const bool on = row < w.end;
+    const int64_t off = row * D;
+    mbar_wait<true>(ring.full + 8u * s, phase, abort_flag, status, kErrTransformWait);
+    const uint32_t at0 = ring.slot(s, 0) + uint32_t(rg.group * D + rg.tg * 8) * 2u;
+    auto piece = [&](int op, int i) {
+      const int pc = rg.tg + i * rg.G;
+      return (on && pc < pieces) ? ld_shared_v4(at0 + uint32_t(op) * op_bytes + uint32_t(i * rg.G) * 16u) : zero4;
+    };
+    F2 rrp = f2(0.f, 0.f);
+    if (post) {   // uniform over the CTA
+      F2 sbb = f2(0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < PP; ++i) {
+        const uint4 bqi = piece(0, i);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const F2 bb = f2_of(word_of(bqi, q));
+          sbb = f2_fma(bb, bb, sbb);
+        }
       }
-      r_p = rsqrtf(__fdiv_rn(warp_sum(ss), float(D)) + eps);
-      if (rstd_post && lane == 0) rstd_post[row] = r_p;
+      float sums[1];
+      {
+        float lo, hi;
+        f2_get(sbb, lo, hi);
+        sums[0] = lo + hi;
+      }
+      group_sum<1>(sums, rg, red, flip);
+      const float r_p = rsqrtf(div_n(sums[0], D, inv_n) + eps);
+      if (on && rstd_post && rg.tg == 0) rstd_post[row] = r_p;
+      rrp = f2(r_p, r_p);
     }
     // x_out = round(x_in + y); its sum of squares is taken over the rounded values
-    float sx = 0.f;
-    for (int pc = lane; pc < pieces; pc += 32) {
-      float b[8], xi[8], xo[8];
-      load8(branch + off + pc * 8, b);
-      load8(x_in + off + pc * 8, xi);
-      if (g_post) {
-        float g[8];
-        load8(g_post + pc * 8, g);
+    uint32_t xo[PP][4];
+    F2 sxx = f2(0.f, 0.f);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float y = norm_y<LEV>(g[e], b[e], r_p);
-          xo[e] = rb(LEV ? __fadd_rn(xi[e], rb(y)) : xi[e] + y);
+    for (int i = 0; i < PP; ++i) {
+      const int pc = rg.tg + i * rg.G;
+      const uint4 bqi = piece(0, i), xqi = piece(1, i);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t bw = word_of(bqi, q), xw = word_of(xqi, q);
+        if (post) {
+          const F2 br = f2_mul(f2_of(bw), rrp);
+          if constexpr (LEV) xo[i][q] = add_bf16x2(xw, mul_bf16x2(word_of(gpq[i], q), bf16x2_of(br)));
+          else xo[i][q] = bf16x2_of(f2_add(f2_of(xw), f2_mul(f2_of(word_of(gpq[i], q)), br)));
+        } else {
+          xo[i][q] = add_bf16x2(xw, bw);
         }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) xo[e] = rb(__fadd_rn(xi[e], b[e]));
+        const F2 xx = f2_of(xo[i][q]);
+        sxx = f2_fma(xx, xx, sxx);
       }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) sx = fmaf(xo[e], xo[e], sx);
-      store8(x_out + off + pc * 8, xo);
+      if (on && pc < pieces)
+        *reinterpret_cast<uint4*>(x_out + off + pc * 8) = make_uint4(xo[i][0], xo[i][1], xo[i][2], xo[i][3]);
     }
-    const float r_n = rsqrtf(__fdiv_rn(warp_sum(sx), float(D)) + eps);
-    if (rstd_next && lane == 0) rstd_next[row] = r_n;
-    if (a_next) {
-      for (int pc = lane; pc < pieces; pc += 32) {   // this lane re-reads the pieces it has just written
-        float xo[8], g[8], o[8];
-        load8(x_out + off + pc * 8, xo);
-        load8(g_next + pc * 8, g);
+    float sx[1];
+    {
+      float lo, hi;
+      f2_get(sxx, lo, hi);
+      sx[0] = lo + hi;
+    }
+    group_sum<1>(sx, rg, red1, flip1);
+    if (threadIdx.x == 0 && !ahead.done(parts)) {   // the slot of the batch before this one takes the batch stages - 1 ahead
+      const int prev = s == 0 ? stages - 1 : s - 1;
+      mbar_wait(ring.empty + 8u * prev, s == 0 ? phase ^ 1u : phase, abort_flag, status, kErrProducerWait);
+      fetch(prev, ahead);
+      ahead.next(rg.groups, T, parts);
+    }
+    // the slot is not read again: hand it back before the output pass
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(ring.empty + 8u * s);
+    if (++s == stages) s = 0, phase ^= 1u;
+    if (on) {
+      const float r_n = rsqrtf(div_n(sx[0], D, inv_n) + eps);
+      if (rstd_next && rg.tg == 0) rstd_next[row] = r_n;
+      if (a_next) {
+        const F2 rrn = f2(r_n, r_n);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = norm_y<LEV>(g[e], xo[e], r_n);
-        store8(a_next + off + pc * 8, o);
+        for (int i = 0; i < PP; ++i) {
+          const int pc = rg.tg + i * rg.G;
+          if (pc < pieces) {
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const F2 xr = f2_mul(f2_of(xo[i][q]), rrn);
+              if constexpr (LEV) o[q] = mul_bf16x2(word_of(gnq[i], q), bf16x2_of(xr));
+              else o[q] = bf16x2_of(f2_mul(f2_of(word_of(gnq[i], q)), xr));
+            }
+            *reinterpret_cast<uint4*>(a_next + off + pc * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
       }
     }
   }
+  if (threadIdx.x == 0 && *abort_flag) __nanosleep(200000);   // an expired wait: let copies in flight land first
 }
 
 // A CTA walks parts of consecutive rows (the partition of norm_partial_rows) in batches, row groups and batch ring as
@@ -348,16 +440,27 @@ void sandwich_tail_fwd(const bf16_t* branch, const bf16_t* x_in, const bf16_t* g
              "sandwich_tail_fwd: branch, x_in, g_next, x_out required; D % 8 == 0");
   NM_REQUIRE(aligned16(branch, x_in, g_post, g_next, x_out, a_next), "sandwich_tail_fwd: every row pointer must be "
                                                                      "16-byte aligned");
+  NM_REQUIRE(D <= kGroupThreads * 4 * 8, "sandwich_tail_fwd: D <= 8192");
   if (T == 0) return;
-  const int grid = int(std::min<int64_t>((T + kRowWarps - 1) / kRowWarps, int64_t(ce::sm_count()) * 8));
+  const bool lev = r == Rounding::Levanter;
+  const int pieces = D / 8;
+  const int pp = pieces_per_thread_for(pieces);
+  const int G = group_threads_for(pieces, pp);
+  const int ctas = pp <= 2 ? 2 : 1;
+  const int64_t parts = norm_partial_rows(T);   // any partition of the rows would do; this one divides evenly over the grid
+  const uint32_t op_bytes = ring_op_bytes(kGroupThreads / G, D);
+  const int stages = ring_stages_for(ctas, 2, op_bytes, 512, 6);
+  const uint32_t smem = ring_bytes(stages, 2, op_bytes);
+  auto kern = pp == 1   ? (lev ? k_sandwich_fwd<true, 1> : k_sandwich_fwd<false, 1>)
+              : pp == 2 ? (lev ? k_sandwich_fwd<true, 2> : k_sandwich_fwd<false, 2>)
+                        : (lev ? k_sandwich_fwd<true, 4> : k_sandwich_fwd<false, 4>);
   auto B = [](const bf16_t* p) { return reinterpret_cast<const __nv_bfloat16*>(p); };
   auto M = [](bf16_t* p) { return reinterpret_cast<__nv_bfloat16*>(p); };
-  if (r == Rounding::Levanter)
-    k_sandwich_fwd<true><<<grid, kRowWarps * 32, 0, st>>>(B(branch), B(x_in), B(g_post), B(g_next), M(x_out), M(a_next),
-                                                          rstd_post, rstd_next, T, D, eps);
-  else
-    k_sandwich_fwd<false><<<grid, kRowWarps * 32, 0, st>>>(B(branch), B(x_in), B(g_post), B(g_next), M(x_out),
-                                                           M(a_next), rstd_post, rstd_next, T, D, eps);
+  NM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  const int grid = int(std::min<int64_t>(parts, int64_t(ce::sm_count()) * ctas));
+  kern<<<grid, kGroupThreads, smem, st>>>(B(branch), B(x_in), B(g_post), B(g_next), M(x_out), M(a_next), rstd_post,
+                                          rstd_next, T, D, eps, parts, G, stages, op_bytes, inv_if_pow2(D),
+                                          row_status_word());
   NM_CUDA(cudaGetLastError());
 }
 

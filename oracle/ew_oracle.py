@@ -112,3 +112,20 @@ def sandwich_bwd_levanter(dx_out, da_next, x_out, g_next, rstd_next, branch, g_p
     ap = bf(np.asarray(g_post, f)[None, :] * dxm)
     sba = (b.astype(np.float64) * ap.astype(np.float64)).sum(1)
     return dxm, db, gcn, gcp, sba
+
+
+def rmsnorm_fwd_levanter(x, gain, r):
+    """out = bf16(g bf16(x r)) for given row statistics r (rmsnorm_kernels.cuh:4; the kernel's r = rsqrtf(ms + eps) is an
+    approximation checked apart)."""
+    f = np.float32
+    return bf(np.asarray(gain, f)[None, :] * bf(np.asarray(x, f) * np.asarray(r, f)[:, None]))
+
+
+def sandwich_fwd_levanter(branch, x_in, g_post, g_next, r_post, r_next):
+    """-> (x_out, a_next) for given statistics: y = g_post ? bf16(g_post bf16(branch r_post)) : branch;
+    x_out = bf16(x_in + y); a_next = bf16(g_next bf16(x_out r_next)) (rmsnorm_kernels.cuh:4,9, k_sandwich_fwd :100-168)."""
+    f = np.float32
+    b = np.asarray(branch, f)
+    y = rmsnorm_fwd_levanter(b, g_post, r_post) if g_post is not None else b
+    x_out = bf(np.asarray(x_in, f) + y)
+    return x_out, rmsnorm_fwd_levanter(x_out, g_next, r_next)

@@ -114,3 +114,68 @@ def test_sandwich_bwd_bits(T, D, post):
     else:
         assert np.array_equal(_bits(dbr), _bits_of(want_in))
     _status_is_zero(L)
+
+
+def _true_rstd(v):
+    return 1.0 / np.sqrt((v.astype(np.float64) ** 2).mean(1) + EPS)
+
+
+@pytest.mark.parametrize("T,D", [(777, 2048), (300, 512), (1500, 1024), (129, 136), (64, 256), (210, 4096), (97, 8192)])
+def test_rmsnorm_fwd_bits(T, D):
+    from gpu_common import lib, nmce
+    import ew_oracle
+    rng = np.random.default_rng(7 * T + D)
+    x = ew_oracle.bf(rng.standard_normal((T, D)).astype(np.float32) * 2)
+    gain = ew_oracle.bf((1 + 0.2 * rng.standard_normal(D)).astype(np.float32))
+    L = lib()
+    d_x, d_g = _dev(x), _dev(gain)
+    y = torch.empty(T, D, dtype=torch.bfloat16, device="cuda")
+    rstd = torch.empty(T, device="cuda")
+    L.nm_rmsnorm_fwd(1, 0, nmce.ptr(d_x), nmce.ptr(d_g), nmce.ptr(y), nmce.ptr(rstd), T, D, EPS, None)
+    torch.cuda.synchronize()
+    r = rstd.cpu().numpy()
+    np.testing.assert_allclose(r, _true_rstd(x), rtol=1e-6)       # f32 sum of 8192 squares + rsqrtf
+    assert np.array_equal(_bits(y), _bits_of(ew_oracle.rmsnorm_fwd_levanter(x, gain, r)))
+    # statistics only (no output): same r
+    rstd2 = torch.empty(T, device="cuda")
+    L.nm_rmsnorm_fwd(1, 0, nmce.ptr(d_x), nmce.ptr(d_g), None, nmce.ptr(rstd2), T, D, EPS, None)
+    torch.cuda.synchronize()
+    assert torch.equal(rstd, rstd2)
+    _status_is_zero(L)
+
+
+@pytest.mark.parametrize("T,D", [(777, 2048), (300, 512), (1500, 1024), (129, 136), (64, 256), (210, 4096), (97, 8192)])
+@pytest.mark.parametrize("post", [True, False])
+def test_sandwich_fwd_bits(T, D, post):
+    from gpu_common import lib, nmce
+    import ew_oracle
+    rng = np.random.default_rng(11 * T + D + int(post))
+    branch = ew_oracle.bf(rng.standard_normal((T, D)).astype(np.float32) * 1.5)
+    x_in = ew_oracle.bf(rng.standard_normal((T, D)).astype(np.float32))
+    gp = ew_oracle.bf((1 + 0.2 * rng.standard_normal(D)).astype(np.float32)) if post else None
+    gn = ew_oracle.bf((1 + 0.2 * rng.standard_normal(D)).astype(np.float32))
+    L = lib()
+    d_b, d_x, d_gn = _dev(branch), _dev(x_in), _dev(gn)
+    d_gp = _dev(gp) if post else None
+    x_out = torch.empty(T, D, dtype=torch.bfloat16, device="cuda")
+    a_next = torch.empty(T, D, dtype=torch.bfloat16, device="cuda")
+    rp = torch.zeros(T, device="cuda")
+    rn = torch.zeros(T, device="cuda")
+    p = nmce.ptr
+    L.nm_sandwich_tail_fwd(1, 0, p(d_b), p(d_x), p(d_gp), p(d_gn), p(x_out), p(a_next), p(rp) if post else None, p(rn),
+                           T, D, EPS, None)
+    torch.cuda.synchronize()
+    r_p, r_n = rp.cpu().numpy(), rn.cpu().numpy()
+    if post:
+        np.testing.assert_allclose(r_p, _true_rstd(branch), rtol=1e-6)
+    want_xo, want_an = ew_oracle.sandwich_fwd_levanter(branch, x_in, gp, gn, r_p if post else None, r_n)
+    assert np.array_equal(_bits(x_out), _bits_of(want_xo))
+    np.testing.assert_allclose(r_n, _true_rstd(want_xo), rtol=1e-6)   # statistics of the stored (rounded) x_out
+    assert np.array_equal(_bits(a_next), _bits_of(want_an))
+    # in place over the residual stream (x_out == x_in): same bits
+    inpl = d_x.clone()
+    an2 = torch.empty_like(a_next)
+    L.nm_sandwich_tail_fwd(1, 0, p(d_b), p(inpl), p(d_gp), p(d_gn), p(inpl), p(an2), None, None, T, D, EPS, None)
+    torch.cuda.synchronize()
+    assert torch.equal(inpl, x_out) and torch.equal(an2, a_next)
+    _status_is_zero(L)
