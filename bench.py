@@ -618,9 +618,9 @@ def main():
     ap.add_argument("--grad-path", type=int, default=-1,
                     help="how dX / dW get the normalised gradient: 0 in-place pass + 128x256 tiles, 1 pass + 256x512 pair "
                          "tiles, 2 formed inside the pair-tile kernels (no pass); -1: chosen per call")
-    ap.add_argument("--tail-order", type=int, default=1,
-                    help="last chunk with a dW reducer: 1 dX first on all SMs, then dW buckets beside the reductions; 0 dW "
-                         "buckets first and dX beside the reductions")
+    ap.add_argument("--tail-order", type=int, default=0,
+                    help="last chunk with a dW reducer: 0 dW buckets first and dX beside their reductions; 1 dX first on "
+                         "all SMs, then dW buckets beside the reductions")
     ap.add_argument("--zero1", action="store_true",
                     help="reduce dW to its owners (reduce-scatter), AdamH on owned elements and all-gather of the bf16 "
                          "head inside every step, instead of the dW all-reduce (the optimizer then is in the timing)")

@@ -90,10 +90,10 @@ int nm_ce_set_cta_pair(int logits, int dgrad, int wgrad);
  * in the reference (its nm_ce_set_backends chooses between its own kernels and cuBLASLt). */
 int nm_ce_set_grad_path(int path);
 
-/* Order of the last chunk of a call whose dW goes through a bucketed reducer: 1 (default) = when dx does not alias x,
- * dX runs first on every SM and only the dW buckets share the GPU with the reductions; 0 = the dW buckets first and dX
- * beside the reductions (always the order when dx aliases x). Results do not depend on it. Process-wide. No
- * counterpart in the reference. */
+/* Order of the last chunk of a call whose dW goes through a bucketed reducer: 0 (default) = the dW buckets first and dX
+ * beside their reductions (always the order when dx aliases x); 1 = when dx does not alias x, dX runs first on every SM
+ * and only the dW buckets share the GPU with the reductions. Results do not depend on it. Process-wide. No counterpart
+ * in the reference. */
 int nm_ce_set_tail_order(int order);
 
 /* One of the tcgen05 contractions alone, for unit tests and ncu (kind 0: C[M,N] f32 = A[M,K] B[N,K]^T, both
