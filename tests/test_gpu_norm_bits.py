@@ -43,7 +43,7 @@ def _status_is_zero(L):
 
 
 @pytest.mark.parametrize("T,D", [(777, 2048), (300, 512), (1500, 1024), (129, 136), (64, 256), (210, 4096), (97, 8192),
-                                 (40, 4104)])
+                                 (40, 4104), (1, 512), (7, 2048), (5000, 8)])
 @pytest.mark.parametrize("with_res", [True, False])
 def test_rmsnorm_bwd_bits(T, D, with_res):
     from gpu_common import lib, nmce
@@ -74,7 +74,8 @@ def test_rmsnorm_bwd_bits(T, D, with_res):
     _status_is_zero(L)
 
 
-@pytest.mark.parametrize("T,D", [(777, 2048), (300, 512), (1500, 1024), (129, 136), (64, 256), (210, 4096), (97, 8192)])
+@pytest.mark.parametrize("T,D", [(777, 2048), (300, 512), (1500, 1024), (129, 136), (64, 256), (210, 4096), (97, 8192),
+                                 (1, 512), (7, 2048)])
 @pytest.mark.parametrize("post", [True, False])
 def test_sandwich_bwd_bits(T, D, post):
     from gpu_common import lib, nmce
@@ -179,3 +180,20 @@ def test_sandwich_fwd_bits(T, D, post):
     torch.cuda.synchronize()
     assert torch.equal(inpl, x_out) and torch.equal(an2, a_next)
     _status_is_zero(L)
+
+
+def test_norm_kernels_reject_rows_longer_than_8192():
+    from gpu_common import lib, nmce
+    L = lib()
+    T, D = 4, 8200
+    a = torch.zeros(T, D, dtype=torch.bfloat16, device="cuda")
+    g = torch.ones(D, dtype=torch.bfloat16, device="cuda")
+    r = torch.ones(T, device="cuda")
+    p = nmce.ptr
+    raw = L.raw   # status codes instead of exceptions
+    assert raw("nm_rmsnorm_fwd")(1, 0, p(a), p(g), p(a), p(r), T, D, EPS, None) == 1
+    assert raw("nm_rmsnorm_bwd_add_partial")(1, 0, p(a), p(a), p(g), p(r), None, p(a), None, T, D, EPS, None) == 1
+    assert raw("nm_sandwich_tail_fwd")(1, 0, p(a), p(a), None, p(g), p(a), p(a), None, p(r), T, D, EPS, None) == 1
+    assert raw("nm_sandwich_tail_bwd_partial")(1, 0, p(a), p(a), p(a), p(g), p(r), p(a), None, None, p(a), p(a), None,
+                                               None, T, D, EPS, None) == 1
+    assert b"8192" in raw("nm_last_error")()
