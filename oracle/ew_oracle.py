@@ -58,7 +58,9 @@ def sum_fixed(x):
 # not contract), `bf` rounds to bf16 (nearest even) and widens again. Row sums are taken in float64 and rounded to f32
 # once: equal to an f32 sum in ANY order whenever all partial sums are exactly representable, which the parity tests
 # arrange by drawing the summed operands from small dyadic grids. The saved statistics r (rstd) are inputs, as in the
-# trainer's call; rsqrtf itself is not restated.
+# trainer's call; rsqrtf itself is not restated. Pinned: tests/golden/norm_golden.npz holds outputs of the reference's own
+# emulation of these kernels (tests/s3/levemu.py:23-44, composed as tests/s3/test_rmsnorm.py:158-176), made by
+# tests/golden/make_norm_golden.py; tests/test_ew_norm_oracle.py checks this restatement against every bit of it.
 def bf(a):
     """float32 array -> float32 array holding the bf16 roundings (nearest, ties to even)."""
     u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)

@@ -69,3 +69,54 @@ def test_sandwich_bwd_levanter_close_to_float64():
     assert _rel(gcn.sum(0, dtype=np.float64), dgn64) < 1e-2 and _rel(gcp.sum(0, dtype=np.float64), dgp64) < 1.2e-2
     dx_in2, dbr2, _, none_p, _ = ew_oracle.sandwich_bwd_levanter(dxo, da, xo, gn, rn.astype(np.float32), None, None, None, EPS)
     assert none_p is None and np.array_equal(dx_in2, dx_in) and np.array_equal(dbr2, dx_in2)
+
+
+# ----------------------------------------------------------------------------- pinned to the reference's own emulation
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "norm_golden.npz")
+
+
+def _f32(bits):
+    """uint16 bf16 bit patterns -> float32 values"""
+    return (np.asarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def _bits(a):
+    return (np.ascontiguousarray(a, np.float32).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def test_oracle_equals_reference_emulation_rmsnorm():
+    """tests/golden/norm_golden.npz holds outputs of the reference's tests/s3/levemu.py (made by
+    tests/golden/make_norm_golden.py): the numpy restatement must reproduce every bit."""
+    G = np.load(GOLDEN)
+    eps = float(G["eps"])
+    for name in ("n512", "n136", "n2048"):
+        x, dy, g, dres = (_f32(G[f"{name}.{k}"]) for k in ("x", "dy", "g", "dres"))
+        r = G[f"{name}.rstd"]
+        assert np.array_equal(_bits(ew_oracle.rmsnorm_fwd_levanter(x, g, r)), G[f"{name}.out"])
+        dx, gc = ew_oracle.rmsnorm_bwd_add_levanter(dy, x, g, r, None, eps)
+        assert np.array_equal(_bits(dx), G[f"{name}.dx"]) and np.array_equal(_bits(gc), G[f"{name}.dgc"])
+        dx2, _ = ew_oracle.rmsnorm_bwd_add_levanter(dy, x, g, r, dres, eps)
+        assert np.array_equal(_bits(dx2), G[f"{name}.dx_res"])
+
+
+def test_oracle_equals_reference_emulation_sandwich():
+    G = np.load(GOLDEN)
+    eps = float(G["eps"])
+    for name, post in (("s512p", True), ("s512", False), ("s136p", True), ("s2048p", True)):
+        b, xi, gn, dan, dxo = (_f32(G[f"{name}.{k}"]) for k in ("b", "xi", "gn", "dan", "dxo"))
+        gp = _f32(G[f"{name}.gp"]) if post else None
+        rp = G[f"{name}.rp"] if post else None
+        rn = G[f"{name}.rn"]
+        xo, an = ew_oracle.sandwich_fwd_levanter(b, xi, gp, gn, rp, rn)
+        assert np.array_equal(_bits(xo), G[f"{name}.x_out"]) and np.array_equal(_bits(an), G[f"{name}.a_next"])
+        dx_in, dbr, gcn, gcp, _ = ew_oracle.sandwich_bwd_levanter(dxo, dan, xo, gn, rn, b if post else None, gp, rp, eps)
+        assert np.array_equal(_bits(dx_in), G[f"{name}.dx_in"]) and np.array_equal(_bits(gcn), G[f"{name}.dgcn"])
+        if post:
+            # the post-norm's row sum of branch * a_post is not on a grid: torch's and numpy's float sums may differ in
+            # the last bit of c, which can move a bf16 rounding of the branch gradient on a few elements by one step
+            got, want = _bits(dbr).astype(np.int32), G[f"{name}.dbranch"].astype(np.int32)
+            off = got != want
+            assert off.mean() < 2e-3 and (np.abs(got - want)[off] <= 1).all()
+            assert np.array_equal(_bits(gcp), G[f"{name}.dgcp"])
+        else:
+            assert np.array_equal(_bits(dbr), G[f"{name}.dx_in"])

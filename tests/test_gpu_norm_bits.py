@@ -197,3 +197,91 @@ def test_norm_kernels_reject_rows_longer_than_8192():
     assert raw("nm_sandwich_tail_bwd_partial")(1, 0, p(a), p(a), p(a), p(g), p(r), p(a), None, None, p(a), p(a), None,
                                                None, T, D, EPS, None) == 1
     assert b"8192" in raw("nm_last_error")()
+
+
+# ----------------------------------------------------------------------------- against the reference's own emulation
+def _golden():
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "norm_golden.npz"))
+
+
+def _dev_bits(bits):
+    """uint16 bf16 bit patterns -> bf16 device tensor"""
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).cuda().view(torch.bfloat16)
+
+
+def _u16(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+@pytest.mark.parametrize("name", ["n512", "n136", "n2048"])
+def test_rmsnorm_pair_equals_reference_emulation(name):
+    """Inputs and outputs of the reference's tests/s3/levemu.py (tests/golden/norm_golden.npz): exact-sum inputs, so the
+    kernels must reproduce every bit of out, dx and bf16(dres + dx); the saved statistics are the emulation's."""
+    from gpu_common import lib, nmce
+    G = _golden()
+    eps = float(G["eps"])
+    x, dy, g, dres = (_dev_bits(G[f"{name}.{k}"]) for k in ("x", "dy", "g", "dres"))
+    r_emu = G[f"{name}.rstd"]
+    T, D = x.shape
+    L = lib()
+    p = nmce.ptr
+    y = torch.empty_like(x)
+    rstd = torch.empty(T, device="cuda")
+    L.nm_rmsnorm_fwd(1, 0, p(x), p(g), p(y), p(rstd), T, D, eps, None)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(rstd.cpu().numpy(), r_emu, rtol=3e-7)     # rsqrtf against torch's CPU rsqrt
+    r_dev = torch.from_numpy(r_emu).cuda()
+    if np.array_equal(rstd.cpu().numpy(), r_emu):
+        assert np.array_equal(_u16(y), G[f"{name}.out"])
+    for res, key in ((None, "dx"), (dres, "dx_res")):
+        dx = torch.empty_like(x)
+        part = torch.zeros(int(L.nm_norm_partial_rows(T)), D, device="cuda")
+        L.nm_rmsnorm_bwd_add_partial(1, 0, p(dy), p(x), p(g), p(r_dev), p(res), p(dx), p(part), T, D, eps, None)
+        torch.cuda.synchronize()
+        assert np.array_equal(_u16(dx), G[f"{name}.{key}"])
+        want = (G[f"{name}.dgc"].astype(np.uint32) << 16).view(np.float32).sum(0, dtype=np.float64)
+        np.testing.assert_allclose(part.sum(0).cpu().numpy(), want, rtol=2e-5, atol=1e-7)
+    _status_is_zero(L)
+
+
+@pytest.mark.parametrize("name,post", [("s512p", True), ("s512", False), ("s136p", True), ("s2048p", True)])
+def test_sandwich_equals_reference_emulation(name, post):
+    from gpu_common import lib, nmce
+    G = _golden()
+    eps = float(G["eps"])
+    b, xi, gn, dan, dxo = (_dev_bits(G[f"{name}.{k}"]) for k in ("b", "xi", "gn", "dan", "dxo"))
+    gp = _dev_bits(G[f"{name}.gp"]) if post else None
+    rn = torch.from_numpy(G[f"{name}.rn"]).cuda()
+    rp = torch.from_numpy(G[f"{name}.rp"]).cuda() if post else None
+    T, D = b.shape
+    L = lib()
+    p = nmce.ptr
+    x_out, a_next = torch.empty_like(b), torch.empty_like(b)
+    rp_k, rn_k = torch.zeros(T, device="cuda"), torch.zeros(T, device="cuda")
+    L.nm_sandwich_tail_fwd(1, 0, p(b), p(xi), p(gp), p(gn), p(x_out), p(a_next), p(rp_k) if post else None, p(rn_k), T, D,
+                           eps, None)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(rn_k.cpu().numpy(), G[f"{name}.rn"], rtol=3e-7)
+    if post:
+        np.testing.assert_allclose(rp_k.cpu().numpy(), G[f"{name}.rp"], rtol=3e-7)
+    if not post or np.array_equal(rp_k.cpu().numpy(), G[f"{name}.rp"]):
+        assert np.array_equal(_u16(x_out), G[f"{name}.x_out"])
+    # the backward from the emulation's stored x_out and statistics
+    xo = _dev_bits(G[f"{name}.x_out"])
+    dx_in, dbr = torch.empty_like(b), torch.empty_like(b)
+    P = int(L.nm_norm_partial_rows(T))
+    pgn, pgp = torch.zeros(P, D, device="cuda"), torch.zeros(P, D, device="cuda")
+    L.nm_sandwich_tail_bwd_partial(1, 0, p(dxo), p(dan), p(xo), p(gn), p(rn), p(b), p(gp), p(rp), p(dx_in), p(dbr), p(pgn),
+                                   p(pgp) if post else None, T, D, eps, None)
+    torch.cuda.synchronize()
+    assert np.array_equal(_u16(dx_in), G[f"{name}.dx_in"])
+    want = (G[f"{name}.dgcn"].astype(np.uint32) << 16).view(np.float32).sum(0, dtype=np.float64)
+    np.testing.assert_allclose(pgn.sum(0).cpu().numpy(), want, rtol=2e-5, atol=1e-7)
+    if post:
+        got, ref = _u16(dbr).astype(np.int32), G[f"{name}.dbranch"].astype(np.int32)
+        off = got != ref
+        assert off.mean() < 5e-3 and (np.abs(got - ref)[off] <= 1).all()
+    else:
+        assert np.array_equal(_u16(dbr), G[f"{name}.dx_in"])
+    _status_is_zero(L)
