@@ -32,6 +32,9 @@ int nm_sandwich_tail_bwd_partial(int dtype, int rounding, const void* dx_out, co
  * library. This reads the word after the stream's work (it synchronises the stream), clears it when set, and returns
  * NM_ERR_DEVICE with the bits in *status_host when it was not 0. */
 int nm_norm_bwd_device_status(void* stream, uint32_t* status_host);
+/* Test hook: a millisecond-bounded wait on a barrier that nothing completes (limit_cycles <= 2e6), pointed at that word:
+ * afterwards nm_norm_bwd_device_status reports what a kernel whose wait ran out would have left. */
+int nm_norm_bwd_test_timeout(int64_t limit_cycles, void* stream);
 
 #ifdef __cplusplus
 }

@@ -359,6 +359,15 @@ int nm_norm_bwd_device_status(void* stream, uint32_t* status_host) {
                             std::to_string(*status_host) + "); the gradients of that call are invalid");
   });
 }
+// Test hook: runs the short bounded-wait probe of nm_ce_test_wait_timeout against the norm kernels' status word, so that
+// the word afterwards holds what a norm backward kernel whose wait ran out would have left.
+int nm_norm_bwd_test_timeout(int64_t limit_cycles, void* stream) {
+  return guarded([&] {
+    uint32_t* word = nm::ew::row_status_word();
+    nm::ce::launch_wait_timeout_probe(word, static_cast<long long>(limit_cycles), reinterpret_cast<int*>(word + 1),
+                                      S(stream));
+  });
+}
 int nm_sum_fixed(const float* x, int64_t n, float* out, void* stream) {
   return guarded([&] { nm::ew::sum_fixed(x, n, out, S(stream)); });
 }

@@ -17,7 +17,7 @@ namespace {
 
 // Where the row kernels whose waits are bounded (the norm backward kernels' batch ring) leave their error bits: one word
 // per GPU, built into the library because those entry points take no workspace.
-static __device__ uint32_t g_row_status_word;
+static __device__ uint32_t g_row_status_word[2];   // [0] the error bits, [1] scratch of the test probe
 std::mutex g_row_status_mu;
 uint32_t* g_row_status_ptr[kMaxDeviceOrdinals] = {};
 

@@ -55,6 +55,7 @@ SIGS = {
     "nm_doc_meta": (I32, [VP, VP, I32, I32, I32, I32, VP, VP, VP, VP, VP, VP, VP, VP]),
     "nm_sum_fixed": (I32, [VP, I64, VP, VP]),
     "nm_norm_bwd_device_status": (I32, [VP, VP]),
+    "nm_norm_bwd_test_timeout": (I32, [I64, VP]),
     "nm_sandwich_tail_bwd_partial": (I32, [I32, I32, VP, VP, VP, VP, VP, VP, VP, VP, VP, VP, VP, VP, I64, I32, F32, VP]),
     "nm_reduce_partials_rows": (I32, [VP, I32, I32, VP, I32, I32, VP]),
     "nm_comm_unique_id": (I32, [VP]),

@@ -336,3 +336,26 @@ def test_rmsnorm_realistic_inputs_levanter_and_accurate(D):
             assert _rel64(yk, out64) <= 1.05 * floor_y and _rel64(dxk, dx64) <= 1.05 * floor_dx
             np.testing.assert_allclose(rstd.cpu().numpy(), r64[:, 0], rtol=1e-6)
     _status_is_zero(L)
+
+
+def test_norm_status_word_reports_an_expired_wait():
+    """A wait of the batch ring that ran out would leave a bit in the per-GPU status word; nm_norm_bwd_device_status must
+    report it once and clear it. The bit is produced the safe way: the millisecond wait probe pointed at that word (no
+    norm kernel is made to wait)."""
+    from gpu_common import lib, nmce
+    L = lib()
+    _status_is_zero(L)
+    L.nm_norm_bwd_test_timeout(1_000_000, None)
+    word = ctypes.c_uint32(0)
+    with pytest.raises(nmce.NmError) as e:
+        L.nm_norm_bwd_device_status(None, ctypes.byref(word))
+    assert e.value.status == 2 and word.value == 4
+    _status_is_zero(L)      # cleared by the read
+    T, D = 64, 512          # and the kernels run as before
+    a = torch.randn(T, D, device="cuda").to(torch.bfloat16)
+    g = torch.ones(D, dtype=torch.bfloat16, device="cuda")
+    y = torch.empty_like(a)
+    r = torch.empty(T, device="cuda")
+    L.nm_rmsnorm_fwd(1, 0, nmce.ptr(a), nmce.ptr(g), nmce.ptr(y), nmce.ptr(r), T, D, EPS, None)
+    torch.cuda.synchronize()
+    _status_is_zero(L)
