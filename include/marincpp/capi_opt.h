@@ -35,6 +35,14 @@ int nm_adam_update(float* p, void* p16, const float* g, float* mu, float* nu, in
 /* nm_grad_reducer_create (capi_ce.h) with a reduction to owners: every bucket is reduce-scattered (f32), rank r keeps
  * the summed gradient on its element range of each bucket only. */
 int nm_grad_reducer_create_owners(void* comm, float* grad, int V, int D, int n_buckets, void** reducer_out);
+/* ZeRO-2 for the vocabulary-sized gradient (declared, not implemented, by the reference: GradReducer::microbatch_done,
+ * include/marincpp/comm.hpp:52-53). Attach an owners reducer to the backward of every microbatch and call
+ * nm_grad_reducer_microbatch_done after each: this rank's owned elements of every bucket are added into owned_acc
+ * (packed, nm_grad_reducer_owned_elems f32) and the whole [V, D] gradient buffer is zeroed for the next microbatch.
+ * nm_grad_reducer_owned_to_grad copies the packed sums back into the owned ranges before the optimizer step. */
+int64_t nm_grad_reducer_owned_elems(void* reducer);
+int nm_grad_reducer_microbatch_done(void* reducer, float* owned_acc, void* stream);
+int nm_grad_reducer_owned_to_grad(void* reducer, const float* owned_acc, void* stream);
 
 /* An updater for the head [V, D]. reducer: NULL (one rank owns everything) or a handle from
  * nm_grad_reducer_create_owners over the same gradient. */

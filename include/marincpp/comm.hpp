@@ -77,6 +77,18 @@ class GradReducer {
   void bucket_ready(int b, cudaStream_t compute);
   void reduce_all(cudaStream_t compute);       // every bucket, after the work already on `compute`
   void wait(cudaStream_t st);                  // st waits for every bucket reduction enqueued so far
+  // ZeRO-2 for this vocabulary-sized gradient (the reference declares it as GradReducer::microbatch_done,
+  // include/marincpp/comm.hpp:52-53, "reduce-scatter those gradients after every microbatch", and does not implement it).
+  // With a reduction to owners, attach the reducer to the backward of EVERY microbatch and call microbatch_done after
+  // each: on `st`, once the bucket reductions enqueued so far are complete, this rank's owned elements of every bucket
+  // are added into `owned_acc` (packed, bucket after bucket, owned_elems() f32) and the whole [V, D] buffer is set to
+  // zero for the next microbatch. A rank's persistent gradient state is then owned_acc alone, 1 / nranks of V * D; the
+  // [V, D] buffer is scratch between microbatches (it can be shared with anything else that is dead by then).
+  int64_t owned_elems() const;
+  void microbatch_done(float* owned_acc, cudaStream_t st);
+  // Before the optimizer step: the packed sums go back into this rank's owned ranges of the gradient buffer, where an
+  // optimizer on owned elements (HeadAdamH) reads them.
+  void owned_to_grad(const float* owned_acc, cudaStream_t st);
  private:
   Comm& comm_;
   float* grad_;

@@ -191,6 +191,7 @@ void launch_dlogits_inplace(const DzArgs& a, cudaStream_t st);
 void launch_finish_microbatch(float* dw, float* dw_mb, int64_t n, cudaStream_t st);
 void launch_zero_cols(void* x, int64_t rows, int D, int from, cudaStream_t st);   // bf16 x[:, from:] = 0
 void launch_sum_scale(const float* w, int64_t n, float mult, float* out, cudaStream_t st);
+void launch_add_f32(float* acc, const float* src, int64_t n, cudaStream_t st);   // acc += src
 void launch_f32_to_bf16(const float* in, void* out, int64_t n, cudaStream_t st);
 void launch_bf16_to_f32(const void* in, float* out, int64_t n, cudaStream_t st);
 // f32 [rows, D] -> bf16 [rows, 3 D] holding (hi, hi, lo) (which == 0) or (hi, lo, hi) (which == 1) per row, so that

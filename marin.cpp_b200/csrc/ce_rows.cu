@@ -244,6 +244,11 @@ __global__ void k_zero_cols_bf16(__nv_bfloat16* x, int64_t rows, int D, int from
     x[(i / wdt) * D + from + i % wdt] = __float2bfloat16_rn(0.f);
 }
 
+// acc += src (the owned slices of a reduce-scattered gradient into a rank's packed accumulator)
+__global__ void k_add_f32(float* __restrict__ acc, const float* __restrict__ src, int64_t n) {
+  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
+    acc[i] = __fadd_rn(acc[i], src[i]);
+}
 __global__ void k_f32_to_bf16(const float* in, __nv_bfloat16* out, int64_t n) {
   for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
     out[i] = __float2bfloat16_rn(in[i]);
@@ -320,6 +325,12 @@ void launch_zero_cols(void* x, int64_t rows, int D, int from, cudaStream_t st) {
 
 void launch_sum_scale(const float* w, int64_t n, float mult, float* out, cudaStream_t st) {
   k_sum_scale<<<1, 1024, 0, st>>>(w, n, mult, out);
+  NM_CUDA(cudaGetLastError());
+}
+
+void launch_add_f32(float* acc, const float* src, int64_t n, cudaStream_t st) {
+  if (n <= 0) return;
+  k_add_f32<<<grid_for(n, 256), 256, 0, st>>>(acc, src, n);
   NM_CUDA(cudaGetLastError());
 }
 

@@ -219,4 +219,41 @@ void GradReducer::reduce_all(cudaStream_t compute) {
 
 void GradReducer::wait(cudaStream_t st) { NM_CUDA(cudaStreamWaitEvent(st, done_, 0)); }
 
+int64_t GradReducer::owned_elems() const {
+  int64_t total = 0;
+  for (int b = 0; b < n_buckets(); ++b) {
+    int64_t off, len;
+    owned_range(b, off, len);
+    total += len;
+  }
+  return total;
+}
+
+void GradReducer::microbatch_done(float* owned_acc, cudaStream_t st) {
+  NM_REQUIRE(to_owners_, "grad reducer: microbatch_done goes with a reduction to owners");
+  NM_REQUIRE(owned_acc != nullptr, "grad reducer: owned_acc required");
+  wait(st);
+  int64_t at = 0;
+  for (int b = 0; b < n_buckets(); ++b) {
+    int64_t off, len;
+    owned_range(b, off, len);
+    ce::launch_add_f32(owned_acc + at, grad_ + off, len, st);
+    at += len;
+  }
+  NM_CUDA(cudaMemsetAsync(grad_, 0, size_t(V_) * size_t(D_) * sizeof(float), st));
+  // the next microbatch's bucket reductions are enqueued behind events recorded on the compute stream after this
+}
+
+void GradReducer::owned_to_grad(const float* owned_acc, cudaStream_t st) {
+  NM_REQUIRE(to_owners_, "grad reducer: owned_to_grad goes with a reduction to owners");
+  NM_REQUIRE(owned_acc != nullptr, "grad reducer: owned_acc required");
+  int64_t at = 0;
+  for (int b = 0; b < n_buckets(); ++b) {
+    int64_t off, len;
+    owned_range(b, off, len);
+    NM_CUDA(cudaMemcpyAsync(grad_ + off, owned_acc + at, size_t(len) * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    at += len;
+  }
+}
+
 }  // namespace nm

@@ -273,6 +273,27 @@ int nm_grad_reducer_create_owners(void* comm, float* grad, int V, int D, int n_b
   });
 }
 
+int64_t nm_grad_reducer_owned_elems(void* reducer) {
+  int64_t n = 0;
+  const int rc = nm::abi::guarded([&] {
+    NM_REQUIRE(reducer, "nm_grad_reducer_owned_elems: reducer required");
+    n = static_cast<nm::GradReducer*>(reducer)->owned_elems();
+  });
+  return rc == NM_OK ? n : 0;
+}
+int nm_grad_reducer_microbatch_done(void* reducer, float* owned_acc, void* stream) {
+  return nm::abi::guarded([&] {
+    NM_REQUIRE(reducer, "nm_grad_reducer_microbatch_done: reducer required");
+    static_cast<nm::GradReducer*>(reducer)->microbatch_done(owned_acc, static_cast<cudaStream_t>(stream));
+  });
+}
+int nm_grad_reducer_owned_to_grad(void* reducer, const float* owned_acc, void* stream) {
+  return nm::abi::guarded([&] {
+    NM_REQUIRE(reducer, "nm_grad_reducer_owned_to_grad: reducer required");
+    static_cast<nm::GradReducer*>(reducer)->owned_to_grad(owned_acc, static_cast<cudaStream_t>(stream));
+  });
+}
+
 int nm_head_adamh_create(int V, int D, void* reducer, void** out) {
   return nm::abi::guarded([&] {
     NM_REQUIRE(out, "nm_head_adamh_create: out required");

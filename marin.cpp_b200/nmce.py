@@ -72,6 +72,9 @@ SIGS = {
     "nm_adam_update": (I32, [VP, VP, VP, VP, VP, I64, I64, I64, F32, F32, F32, F32, F32, I32, F32, VP, VP, VP, I32,
                              VP]),
     "nm_grad_reducer_create_owners": (I32, [VP, VP, I32, I32, I32, VP]),
+    "nm_grad_reducer_owned_elems": (I64, [VP]),
+    "nm_grad_reducer_microbatch_done": (I32, [VP, VP, VP]),
+    "nm_grad_reducer_owned_to_grad": (I32, [VP, VP, VP]),
     "nm_head_adamh_create": (I32, [I32, I32, VP, VP]),
     "nm_head_adamh_destroy": (I32, [VP]),
     "nm_head_adamh_owned_elems": (I64, [VP]),
@@ -83,7 +86,7 @@ SIGS = {
     "nm_head_adamh_scalars": (I32, [VP, VP, VP]),
 }
 NO_STATUS = {"nm_version", "nm_last_error", "nm_device_arch", "nm_ce_workspace_bytes", "nm_ce_set_backends",
-             "nm_ce_device_arch", "nm_ce_set_fast_stats_exp", "nm_ce_sampled_stride", "nm_ce_sampled_workspace_bytes", "nm_norm_partial_rows", "nm_head_adamh_owned_elems", "nm_ce_suggest_chunk_rows"}
+             "nm_ce_device_arch", "nm_ce_set_fast_stats_exp", "nm_ce_sampled_stride", "nm_ce_sampled_workspace_bytes", "nm_norm_partial_rows", "nm_head_adamh_owned_elems", "nm_grad_reducer_owned_elems", "nm_ce_suggest_chunk_rows"}
 
 IMPLS = {"A": 0, "B1": 1, "B1.5": 2, "B2": 3}
 LEV, ACC = 0, 1

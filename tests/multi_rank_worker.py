@@ -96,6 +96,45 @@ def main():
             print(f"nccl world {world} reduce dtype {reduce_dtype}: dW rel {r:.2e}")
         dist.barrier()
         lib.nm_grad_reducer_destroy(red)
+    # ZeRO-2 for the head gradient: two microbatches per rank, an owners reducer attached to each, microbatch_done after
+    # each. This rank's packed accumulator must equal its owned ranges of the all-rank, all-microbatch dW (computed by
+    # every rank on all rows with plain calls; f32 sums in another order: 1e-5).
+    dw = torch.zeros(V, D, dtype=torch.float32, device=dev)
+    red = ctypes.c_void_p()
+    lib.nm_grad_reducer_create_owners(comm, nmce.ptr(dw), V, D, 4, ctypes.byref(red))
+    n_owned = int(lib.nm_grad_reducer_owned_elems(red))
+    assert n_owned * world == V * D
+    acc = torch.zeros(n_owned, dtype=torch.float32, device=dev)
+    half = n // 2
+    for m in range(2):
+        rs = slice(m * half, (m + 1) * half)
+        dx = torch.empty_like(X[rs])
+        nmce.ce_call(lib, "B1", X[rs].contiguous(), W, Y[rs].contiguous(), WT[rs].contiguous(), gs, dx=dx, dw=dw, chunk=512,
+                     z_loss=1e-4, ignore_index=-100, reducer=red)
+        lib.nm_grad_reducer_microbatch_done(red, nmce.ptr(acc), None)
+    torch.cuda.synchronize()
+    assert not dw.any()
+    XF = torch.from_numpy(x).to(dev).bfloat16()
+    YF, WF = torch.from_numpy(y).to(dev), torch.from_numpy(wt).to(dev)
+    dwf = torch.zeros(V, D, dtype=torch.float32, device=dev)
+    nmce.ce_call(lib, "B1", XF, W, YF, WF, gs, dx=torch.empty_like(XF), dw=dwf, chunk=512, z_loss=1e-4, ignore_index=-100)
+    v0 = (ctypes.c_int * 8)()
+    v1 = (ctypes.c_int * 8)()
+    nb = ctypes.c_int(0)
+    lib.nm_grad_bucket_ranges(V, 4, v0, v1, ctypes.byref(nb))
+    want = []
+    for b in range(nb.value):
+        nelem = (v1[b] - v0[b]) * D
+        own = nelem // world
+        flat = dwf[v0[b]:v1[b]].reshape(-1)
+        want.append(flat[rank * own:(rank + 1) * own])
+    want = torch.cat(want)
+    torch.cuda.synchronize()
+    r = float((acc.double() - want.double()).norm() / want.double().norm())
+    assert r < 1e-5, f"ZeRO-2 owned accumulator vs all-rank dW: rel {r}"
+    print(f"nccl world {world} zero2 rank {rank}: owned accumulator rel {r:.2e}")
+    dist.barrier()
+    lib.nm_grad_reducer_destroy(red)
     lib.nm_comm_destroy(comm)
     dist.destroy_process_group()
 

@@ -324,6 +324,49 @@ def test_one_rank_reducer_attached_to_the_call():
         lib().nm_comm_destroy(comm)
 
 
+def test_one_rank_zero2_accumulates_owned_slices():
+    """ZeRO-2 for the head gradient on a communicator of one rank (reduce-scatter over one rank: the identity): an owners
+    reducer attached to every microbatch, nm_grad_reducer_microbatch_done after each. The packed accumulator must hold
+    the sum of the microbatches' dW (bit for bit here: every microbatch is one chunk, so each element receives the same
+    additions in the same order as in a plain call that accumulates all microbatches into one buffer), the [V, D]
+    buffer must be zero afterwards, and nm_grad_reducer_owned_to_grad must put the sums back where an optimizer on
+    owned elements reads them."""
+    from gpu_common import O, grad_scale_dev, lib, nmce, run_ce, same_bits, to_dev
+    D, V, chunk, micro = 512, 8256, 2048, 3
+    rows = [1500, 2048, 700]
+    idbuf = torch.zeros(128, dtype=torch.uint8)
+    lib().nm_comm_unique_id(nmce.ptr(idbuf))
+    comm = ctypes.c_void_p()
+    lib().nm_comm_create(nmce.ptr(idbuf), 1, 0, ctypes.byref(comm))
+    dw = torch.zeros(V, D, dtype=torch.float32, device="cuda")
+    plain_dw = torch.zeros(V, D, dtype=torch.float32, device="cuda")
+    red = ctypes.c_void_p()
+    lib().nm_grad_reducer_create_owners(comm, nmce.ptr(dw), V, D, 5, ctypes.byref(red))
+    try:
+        n_owned = int(lib().nm_grad_reducer_owned_elems(red))
+        assert n_owned == V * D
+        acc = torch.zeros(n_owned, dtype=torch.float32, device="cuda")
+        for m in range(micro):
+            x, w, y, wt = O.make_inputs(rows[m], D, V, seed=300 + m, ignore_frac=0.05)
+            if m:
+                w = w0
+            w0 = w
+            X, W, Y, WT = to_dev(x, w, y, wt)
+            gs = grad_scale_dev(WT)
+            run_ce(X, W, Y, WT, gs, chunk=chunk, z_loss=1e-4, dw=plain_dw)            # accumulates across microbatches
+            run_ce(X, W, Y, WT, gs, chunk=chunk, z_loss=1e-4, dw=dw, reducer=red)
+            lib().nm_grad_reducer_microbatch_done(red, nmce.ptr(acc), None)
+            torch.cuda.synchronize()
+            assert not dw.any(), "the gradient buffer must be zero after microbatch_done"
+        assert same_bits(acc.view(V, D), plain_dw)
+        lib().nm_grad_reducer_owned_to_grad(red, nmce.ptr(acc), None)
+        torch.cuda.synchronize()
+        assert same_bits(dw, plain_dw)
+    finally:
+        lib().nm_grad_reducer_destroy(red)
+        lib().nm_comm_destroy(comm)
+
+
 def test_two_host_threads_call_concurrently():
     """Two host threads, each with its own stream, workspace and outputs, issue the same call on one GPU at the same
     time (the reference's trainer enters the library from one thread per GPU, src/train/trainer.cpp:57,209-219; here the

@@ -50,6 +50,7 @@ def test_bucketed_dw_allreduce_matches_single_gpu():
         pytest.skip("needs 2 GPUs")
     out = _launch("nccl", 2, 29612)
     assert "reduce dtype 0" in out and "reduce dtype 1" in out
+    assert "zero2 rank 0" in out and "zero2 rank 1" in out      # ZeRO-2: owned accumulators of both ranks checked
 
 
 @pytest.mark.gpu
