@@ -259,11 +259,14 @@ __device__ __forceinline__ void write_gain_partial(const F2 (&dg)[PP][4], const 
 }
 
 // ------------------------------------------------------------------------------------------------ batch ring
-// The backward kernels walk the batches (256 / G consecutive rows) of their parts in order. Thread 0 keeps the next
-// `stages - 1` batches of every row operand on their way into a ring in shared memory, one bulk copy per operand and
-// batch (the rows of a batch are contiguous in memory), so the HBM reads in flight are set by the depth of the ring and
-// not by how many loads a thread can park in registers. A thread copies its pieces of a landed batch into registers and
-// its warp then gives the slot back (one arrive per warp), so a slot is busy for a few hundred cycles only.
+// The norm kernels (forward and backward) walk the batches (256 / G consecutive rows) of their parts in order. Thread 0
+// keeps the next `stages - 1` batches of every row operand on their way into a ring in shared memory, one bulk copy per
+// operand and batch (the rows of a batch are contiguous in memory), so the HBM reads in flight are set by the depth of
+// the ring and not by how many loads a thread can park in registers. A thread reads its pieces of the landed batch from
+// the slot in every pass that needs them (nothing is held in registers across the row sums) and its warp gives the slot
+// back when it has read it for the last time (one arrive per warp). Every wait is bounded (ptx.cuh mbar_wait): one that
+// runs out sets the CTA's abort flag and a bit in the status word; the CTA then runs through its remaining batches
+// without waiting (its outputs are garbage, flagged by the word) and leaves after a pause for the copies in flight.
 struct BatchWalk {
   int64_t row, end;   // first row of the current batch; end of the current part
   int part;
