@@ -88,6 +88,7 @@ template <bool kSuspend = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status,
                                           uint32_t err, long long limit_cycles = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag) return false;            // the CTA has given up already: no point in polling
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
@@ -111,6 +112,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                   uint32_t* status, uint32_t err, long long limit_cycles = kWaitCycles) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
+  if (*abort_flag) return false;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
