@@ -38,9 +38,11 @@ int nm_fused_linear_ce(int impl, int rounding, int io, int logits_store, const v
 
 /* ---- the step on either side of the fused CE (reference include/marincpp/capi.h:29-31, 36-48): the metadata kernel
  *      that produces targets and weights, the RMSNorm pair of the readout head, and the sandwich tail whose forward
- *      produces the CE input (final norm) and whose backward consumes the CE's dX. dtype 1 = bf16 storage only.
+ *      produces the CE input (final norm) and whose backward consumes the CE's dX. dtype: storage of the row tensors
+ *      and gains, 1 = bf16 (the model's; the tuned kernels), 0 = f32 (f32 throughout, both rounding modes alike: the
+ *      reference's own tests use it to tell math errors from rounding).
  *      dgain / dg_next / dg_post: f32 [D], overwritten with the fixed-order reduction of the per-part partials,
- *      rounded to bf16 under levanter rounding; NULL skips it (these entry points make a stream-ordered allocation
+ *      rounded to bf16 under levanter rounding with bf16 storage; NULL skips it (these entry points make a stream-ordered allocation
  *      for the partials, as the reference's test entry points do) ------------------------------------------------ */
 int nm_doc_meta(const int32_t* tokens, const uint8_t* row_valid, int rows, int S, int32_t eos, int max_segs,
                 int32_t* targets, float* weight, int32_t* pos, int32_t* cu_seqlens, int32_t* n_segs,

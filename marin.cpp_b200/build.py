@@ -17,7 +17,7 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libmarincpp_kernels.so")
 ARCHIVE = os.path.join(HERE, "libmarincpp_ce.a")
 SOURCES = ["nm_core.cpp", "ce_api.cpp", "capi_ce.cpp", "comm.cpp", "ce_gemm.cu", "ce_grad_wide.cu", "ce_sampled.cu", "ce_rows.cu", "ew_rmsnorm.cu",
-           "ce_static_ws.cu", "ew_sandwich.cu", "ew_misc.cu", "opt_adamh.cu", "opt_api.cpp"]
+           "ce_static_ws.cu", "ew_sandwich.cu", "ew_norm_f32.cu", "ew_misc.cu", "opt_adamh.cu", "opt_api.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # The norm kernels restate rounding points one IEEE operation at a time: no multiply-add contraction in their units.

@@ -259,7 +259,10 @@ int nm_ce_test_gemm(int kind, const void* a, int64_t lda, const void* b, int64_t
 int nm_rmsnorm_fwd(int dtype, int rounding, const void* x, const void* gain, void* y, float* rstd, int64_t T, int D,
                    float eps, void* stream) {
   return guarded([&] {
-    NM_REQUIRE(dtype == 1, "nm_rmsnorm_fwd: bf16 storage (dtype 1) only");
+    if (dtype == 0)
+      return nm::ew::rmsnorm_fwd_f32(static_cast<const float*>(x), static_cast<const float*>(gain), static_cast<float*>(y),
+                                     rstd, T, D, eps, S(stream));
+    NM_REQUIRE(dtype == 1, "nm_rmsnorm_fwd: storage 0 (f32) or 1 (bf16)");
     nm::ew::rmsnorm_fwd(static_cast<const nm::bf16_t*>(x), static_cast<const nm::bf16_t*>(gain),
                         static_cast<nm::bf16_t*>(y), rstd, T, D, eps, S(stream), rounding_of(rounding));
   });
@@ -272,7 +275,11 @@ int nm_rmsnorm_bwd_add_partial(int dtype, int rounding, const void* dy, const vo
                                const float* rstd, const void* dres, void* dx, float* dgain_partial, int64_t T, int D,
                                float eps, void* stream) {
   return guarded([&] {
-    NM_REQUIRE(dtype == 1, "nm_rmsnorm_bwd_add_partial: bf16 storage (dtype 1) only");
+    if (dtype == 0)
+      return nm::ew::rmsnorm_bwd_add_f32(static_cast<const float*>(dy), static_cast<const float*>(x),
+                                         static_cast<const float*>(gain), rstd, static_cast<const float*>(dres),
+                                         static_cast<float*>(dx), dgain_partial, T, D, eps, S(stream));
+    NM_REQUIRE(dtype == 1, "nm_rmsnorm_bwd_add_partial: storage 0 (f32) or 1 (bf16)");
     nm::ew::rmsnorm_bwd_add(static_cast<const nm::bf16_t*>(dy), static_cast<const nm::bf16_t*>(x),
                             static_cast<const nm::bf16_t*>(gain), rstd, static_cast<const nm::bf16_t*>(dres),
                             static_cast<nm::bf16_t*>(dx), dgain_partial, T, D, eps, S(stream), rounding_of(rounding));
@@ -282,16 +289,22 @@ int nm_rmsnorm_bwd_add_partial(int dtype, int rounding, const void* dy, const vo
 int nm_rmsnorm_bwd_add(int dtype, int rounding, const void* dy, const void* x, const void* gain, const float* rstd,
                        const void* dres, void* dx, float* dgain, int64_t T, int D, float eps, void* stream) {
   return guarded([&] {
-    NM_REQUIRE(dtype == 1, "nm_rmsnorm_bwd_add: bf16 storage (dtype 1) only");
+    NM_REQUIRE(dtype == 0 || dtype == 1, "nm_rmsnorm_bwd_add: storage 0 (f32) or 1 (bf16)");
     const nm::Rounding r = rounding_of(rounding);
     const int64_t rows = nm::ew::norm_partial_rows(T);
     float* part = nullptr;   // test path, as in the reference: the partial buffer is a stream-ordered allocation
     if (dgain) NM_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&part), size_t(rows) * D * 4, S(stream)));
-    nm::ew::rmsnorm_bwd_add(static_cast<const nm::bf16_t*>(dy), static_cast<const nm::bf16_t*>(x),
-                            static_cast<const nm::bf16_t*>(gain), rstd, static_cast<const nm::bf16_t*>(dres),
-                            static_cast<nm::bf16_t*>(dx), part, T, D, eps, S(stream), r);
+    if (dtype == 0)
+      nm::ew::rmsnorm_bwd_add_f32(static_cast<const float*>(dy), static_cast<const float*>(x),
+                                  static_cast<const float*>(gain), rstd, static_cast<const float*>(dres),
+                                  static_cast<float*>(dx), part, T, D, eps, S(stream));
+    else
+      nm::ew::rmsnorm_bwd_add(static_cast<const nm::bf16_t*>(dy), static_cast<const nm::bf16_t*>(x),
+                              static_cast<const nm::bf16_t*>(gain), rstd, static_cast<const nm::bf16_t*>(dres),
+                              static_cast<nm::bf16_t*>(dx), part, T, D, eps, S(stream), r);
     if (dgain) {
-      nm::ew::reduce_partials_rows(part, int(rows), D, dgain, false, r == nm::Rounding::Levanter, S(stream));
+      // the reduced gain gradient is a bf16 value only where the gains are stored in bf16 under levanter rounding
+      nm::ew::reduce_partials_rows(part, int(rows), D, dgain, false, dtype == 1 && r == nm::Rounding::Levanter, S(stream));
       NM_CUDA(cudaFreeAsync(part, S(stream)));
     }
   });
@@ -300,7 +313,11 @@ int nm_sandwich_tail_fwd(int dtype, int rounding, const void* branch, const void
                          const void* g_next, void* x_out, void* a_next, float* rstd_post, float* rstd_next, int64_t T,
                          int D, float eps, void* stream) {
   return guarded([&] {
-    NM_REQUIRE(dtype == 1, "nm_sandwich_tail_fwd: bf16 storage (dtype 1) only");
+    auto F = [](const void* p) { return static_cast<const float*>(p); };
+    if (dtype == 0)
+      return nm::ew::sandwich_tail_fwd_f32(F(branch), F(x_in), F(g_post), F(g_next), static_cast<float*>(x_out),
+                                           static_cast<float*>(a_next), rstd_post, rstd_next, T, D, eps, S(stream));
+    NM_REQUIRE(dtype == 1, "nm_sandwich_tail_fwd: storage 0 (f32) or 1 (bf16)");
     auto B = [](const void* p) { return static_cast<const nm::bf16_t*>(p); };
     nm::ew::sandwich_tail_fwd(B(branch), B(x_in), B(g_post), B(g_next), static_cast<nm::bf16_t*>(x_out),
                               static_cast<nm::bf16_t*>(a_next), rstd_post, rstd_next, T, D, eps, S(stream),
@@ -312,7 +329,7 @@ int nm_sandwich_tail_bwd(int dtype, int rounding, const void* dx_out, const void
                          const float* rstd_post, void* dx_in, void* dbranch, float* dg_next, float* dg_post,
                          int64_t T, int D, float eps, void* stream) {
   return guarded([&] {
-    NM_REQUIRE(dtype == 1, "nm_sandwich_tail_bwd: bf16 storage (dtype 1) only");
+    NM_REQUIRE(dtype == 0 || dtype == 1, "nm_sandwich_tail_bwd: storage 0 (f32) or 1 (bf16)");
     const nm::Rounding r = rounding_of(rounding);
     const int64_t rows = nm::ew::norm_partial_rows(T);
     float* part = nullptr;   // test path: two partial buffers in one stream-ordered allocation
@@ -321,10 +338,16 @@ int nm_sandwich_tail_bwd(int dtype, int rounding, const void* dx_out, const void
     float* pn = part;
     float* pp = part + size_t(rows) * D;
     auto B = [](const void* p) { return static_cast<const nm::bf16_t*>(p); };
-    nm::ew::sandwich_tail_bwd(B(dx_out), B(da_next), B(x_out), B(g_next), rstd_next, B(branch), B(g_post), rstd_post,
-                              static_cast<nm::bf16_t*>(dx_in), static_cast<nm::bf16_t*>(dbranch), dg_next ? pn : nullptr,
-                              (dg_post && g_post) ? pp : nullptr, T, D, eps, S(stream), r);
-    const bool rbf = r == nm::Rounding::Levanter;
+    auto F = [](const void* p) { return static_cast<const float*>(p); };
+    if (dtype == 0)
+      nm::ew::sandwich_tail_bwd_f32(F(dx_out), F(da_next), F(x_out), F(g_next), rstd_next, F(branch), F(g_post), rstd_post,
+                                    static_cast<float*>(dx_in), static_cast<float*>(dbranch), dg_next ? pn : nullptr,
+                                    (dg_post && g_post) ? pp : nullptr, T, D, eps, S(stream));
+    else
+      nm::ew::sandwich_tail_bwd(B(dx_out), B(da_next), B(x_out), B(g_next), rstd_next, B(branch), B(g_post), rstd_post,
+                                static_cast<nm::bf16_t*>(dx_in), static_cast<nm::bf16_t*>(dbranch), dg_next ? pn : nullptr,
+                                (dg_post && g_post) ? pp : nullptr, T, D, eps, S(stream), r);
+    const bool rbf = dtype == 1 && r == nm::Rounding::Levanter;
     if (dg_next) nm::ew::reduce_partials_rows(pn, int(rows), D, dg_next, false, rbf, S(stream));
     if (dg_post && g_post) nm::ew::reduce_partials_rows(pp, int(rows), D, dg_post, false, rbf, S(stream));
     if (want_partials) NM_CUDA(cudaFreeAsync(part, S(stream)));
@@ -335,7 +358,12 @@ int nm_sandwich_tail_bwd_partial(int dtype, int rounding, const void* dx_out, co
                                  const float* rstd_post, void* dx_in, void* dbranch, float* pg_next, float* pg_post,
                                  int64_t T, int D, float eps, void* stream) {
   return guarded([&] {
-    NM_REQUIRE(dtype == 1, "nm_sandwich_tail_bwd_partial: bf16 storage (dtype 1) only");
+    auto F = [](const void* p) { return static_cast<const float*>(p); };
+    if (dtype == 0)
+      return nm::ew::sandwich_tail_bwd_f32(F(dx_out), F(da_next), F(x_out), F(g_next), rstd_next, F(branch), F(g_post),
+                                           rstd_post, static_cast<float*>(dx_in), static_cast<float*>(dbranch), pg_next,
+                                           pg_post, T, D, eps, S(stream));
+    NM_REQUIRE(dtype == 1, "nm_sandwich_tail_bwd_partial: storage 0 (f32) or 1 (bf16)");
     auto B = [](const void* p) { return static_cast<const nm::bf16_t*>(p); };
     nm::ew::sandwich_tail_bwd(B(dx_out), B(da_next), B(x_out), B(g_next), rstd_next, B(branch), B(g_post), rstd_post,
                               static_cast<nm::bf16_t*>(dx_in), static_cast<nm::bf16_t*>(dbranch), pg_next, pg_post, T, D,

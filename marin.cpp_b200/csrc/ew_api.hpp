@@ -44,6 +44,18 @@ void sandwich_tail_bwd(const bf16_t* dx_out, const bf16_t* da_next, const bf16_t
                        bf16_t* dx_in, bf16_t* dbranch, float* pg_next, float* pg_post, int64_t T, int D, float eps,
                        cudaStream_t st, Rounding r = Rounding::Levanter);
 
+// f32-storage forms (ew_norm_f32.cu): the same entry points for float tensors and gains, f32 throughout (both rounding
+// modes coincide); the reference's tests use them to tell math errors from rounding. Not a hot path.
+void rmsnorm_fwd_f32(const float* x, const float* gain, float* y, float* rstd, int64_t T, int D, float eps, cudaStream_t st);
+void rmsnorm_bwd_add_f32(const float* dy, const float* x, const float* gain, const float* rstd, const float* dres, float* dx,
+                         float* dgain_partial, int64_t T, int D, float eps, cudaStream_t st);
+void sandwich_tail_fwd_f32(const float* branch, const float* x_in, const float* g_post, const float* g_next, float* x_out,
+                           float* a_next, float* rstd_post, float* rstd_next, int64_t T, int D, float eps, cudaStream_t st);
+void sandwich_tail_bwd_f32(const float* dx_out, const float* da_next, const float* x_out, const float* g_next,
+                           const float* rstd_next, const float* branch, const float* g_post, const float* rstd_post,
+                           float* dx_in, float* dbranch, float* pg_next, float* pg_post, int64_t T, int D, float eps,
+                           cudaStream_t st);
+
 // The word the norm backward kernels OR their error bits into when one of their bounded waits runs out (one per GPU,
 // zero-initialised, address looked up on first use: make the first backward call on a device outside a stream capture).
 // read_row_status copies it to the host after the stream's work, clears it when set, and returns it.

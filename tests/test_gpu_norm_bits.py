@@ -359,3 +359,61 @@ def test_norm_status_word_reports_an_expired_wait():
     L.nm_rmsnorm_fwd(1, 0, nmce.ptr(a), nmce.ptr(g), nmce.ptr(y), nmce.ptr(r), T, D, EPS, None)
     torch.cuda.synchronize()
     _status_is_zero(L)
+
+
+# ----------------------------------------------------------------------------- f32 storage (math against float64)
+def _norm64(x, g):
+    return x * torch.rsqrt((x * x).mean(dim=1, keepdim=True) + EPS) * g
+
+
+@pytest.mark.parametrize("D", [512, 136, 2048])
+@pytest.mark.parametrize("post", [True, False])
+def test_f32_storage_norm_kernels_against_float64(D, post):
+    """The f32-storage instantiations (storage 0): f32 throughout, so every output is held to 1e-6 of float64 autograd
+    (the reference's bound for them, tests/s3/test_rmsnorm.py:4), with both rounding arguments."""
+    from gpu_common import lib, nmce, rel
+    T = 333
+    g = torch.Generator(device="cuda").manual_seed(D + int(post))
+    rnd = lambda *s, k=1.0: (torch.randn(*s, generator=g, device="cuda") * k).float()
+    x, b = rnd(T, D, k=2.0), rnd(T, D, k=1.5)
+    gn, gp = 1.0 + 0.2 * rnd(D), (1.0 + 0.2 * rnd(D)) if post else None
+    dy, dres, dxo = rnd(T, D, k=1e-2), rnd(T, D, k=1e-2), rnd(T, D, k=1e-2)
+    L = lib()
+    p = nmce.ptr
+    P = int(L.nm_norm_partial_rows(T))
+    # RMSNorm pair
+    x64, g64 = x.double().requires_grad_(True), gn.double().requires_grad_(True)
+    o64 = _norm64(x64, g64)
+    o64.backward(dy.double())
+    for rounding in (0, 1):
+        y, rstd, dx = torch.empty_like(x), torch.empty(T, device="cuda"), torch.empty_like(x)
+        dg = torch.zeros(D, device="cuda")
+        L.nm_rmsnorm_fwd(0, rounding, p(x), p(gn), p(y), p(rstd), T, D, EPS, None)
+        L.nm_rmsnorm_bwd_add(0, rounding, p(dy), p(x), p(gn), p(rstd), p(dres), p(dx), p(dg), T, D, EPS, None)
+        torch.cuda.synchronize()
+        assert rel(y, o64.detach()) < 1e-6 and rel(dx, x64.grad + dres.double()) < 1e-6 and rel(dg, g64.grad) < 1e-6
+        assert rel(rstd, torch.rsqrt((x.double() ** 2).mean(1) + EPS)) < 1e-6
+        part = torch.zeros(P, D, device="cuda")
+        inpl = dres.clone()     # in place over the residual gradient, statistics recomputed (rstd = NULL)
+        L.nm_rmsnorm_bwd_add_partial(0, rounding, p(dy), p(x), p(gn), None, p(inpl), p(inpl), p(part), T, D, EPS, None)
+        torch.cuda.synchronize()
+        assert rel(inpl, x64.grad + dres.double()) < 1e-6 and rel(part.sum(0), g64.grad) < 1e-6
+    # sandwich tail
+    b64, xi64 = b.double().requires_grad_(True), x.double().requires_grad_(True)
+    gp64 = gp.double().requires_grad_(True) if post else None
+    gn64 = gn.double().requires_grad_(True)
+    xo64 = xi64 + (_norm64(b64, gp64) if post else b64)
+    an64 = _norm64(xo64, gn64)
+    ((an64 * dy.double()).sum() + (xo64 * dxo.double()).sum()).backward()
+    x_out, a_next, dx_in, dbr = (torch.empty_like(x) for _ in range(4))
+    rp, rn = torch.empty(T, device="cuda"), torch.empty(T, device="cuda")
+    dgn, dgp = torch.zeros(D, device="cuda"), torch.zeros(D, device="cuda")
+    L.nm_sandwich_tail_fwd(0, 0, p(b), p(x), p(gp), p(gn), p(x_out), p(a_next), p(rp) if post else None, p(rn), T, D, EPS, None)
+    L.nm_sandwich_tail_bwd(0, 0, p(dxo), p(dy), p(x_out), p(gn), p(rn), p(b), p(gp), p(rp) if post else None, p(dx_in),
+                           p(dbr), p(dgn), p(dgp) if post else None, T, D, EPS, None)
+    torch.cuda.synchronize()
+    assert rel(x_out, xo64.detach()) < 1e-6 and rel(a_next, an64.detach()) < 1e-6
+    assert rel(dx_in, xi64.grad) < 2e-6 and rel(dbr, b64.grad) < 2e-6 and rel(dgn, gn64.grad) < 2e-6
+    if post:
+        assert rel(dgp, gp64.grad) < 2e-6
+    _status_is_zero(L)
