@@ -146,3 +146,47 @@ def test_readout_against_float64_autograd():
     r_s, r_g, r_w = rel(ds, st.grad), rel(pp.sum(0), gn.grad), rel(dw, W64.grad)
     print(f"[parity] readout vs f64 autograd: d_state rel {r_s:.2e} dgain rel {r_g:.2e} dW rel {r_w:.2e}")
     assert r_s < 2e-2 and r_g < 2e-2 and r_w < 2e-2     # the reference's bars for this check (test_ce.py:459)
+
+
+def test_readout_in_a_cuda_graph():
+    """The whole readout (RMSNorm forward on the batch ring, fused CE, RMSNorm backward with gain partials) captured into
+    a CUDA graph after one eager call on the device (the norm kernels look up their status word on first use) and
+    replayed: the replay must give the eager call's bits, and the norm status word must stay clear."""
+    import ctypes
+    from gpu_common import lib, nmce, same_bits
+    V, D, T, chunk = 8256, 512, 2100, 1024
+    g, state, gain, W, tg, w, gs = _inputs(T, D, V, seed=21)
+    L = lib()
+    P = L.nm_norm_partial_rows(T)
+    ws = torch.empty(L.nm_ce_workspace_bytes(1, T, D, V, chunk, 1) + 256, dtype=torch.uint8, device="cuda")
+    d0 = (torch.randn(T, D, generator=g, device="cuda") * 1e-3).to(torch.bfloat16)
+
+    def buffers():
+        return dict(nout=torch.empty_like(state), nr=torch.empty(T, device="cuda"),
+                    dw=torch.zeros(V, D, dtype=torch.float32, device="cuda"), ds=d0.clone(),
+                    pp=torch.zeros(P, D, dtype=torch.float32, device="cuda"), loss=torch.empty(T, device="cuda"),
+                    lse=torch.empty(T, device="cuda"))
+
+    def call(o, stream):
+        L.nm_ce_readout(1, nmce.LEV, 1, nmce.ptr(state), nmce.ptr(gain), nmce.ptr(o["nr"]), nmce.ptr(o["nout"]),
+                        nmce.ptr(W), nmce.ptr(o["dw"]), nmce.ptr(o["pp"]), nmce.ptr(gs), nmce.ptr(o["ds"]), D, nmce.ptr(tg),
+                        nmce.ptr(w), nmce.ptr(o["loss"]), nmce.ptr(o["lse"]), None, 0, T, D, V, chunk, EPS, nmce.ptr(ws),
+                        stream)
+
+    eager = buffers()
+    call(eager, None)
+    torch.cuda.synchronize()
+    captured = buffers()
+    s = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=s):
+        call(captured, s.cuda_stream)
+    for _ in range(2):                      # replayed twice from the same starting values
+        captured["dw"].zero_()
+        captured["ds"].copy_(d0)
+        graph.replay()
+    torch.cuda.synchronize()
+    for k in ("loss", "lse", "dw", "ds", "pp", "nr"):
+        assert same_bits(captured[k], eager[k]), f"graph replay differs from the eager call: {k}"
+    word = ctypes.c_uint32(1)
+    assert L.nm_norm_bwd_device_status(None, ctypes.byref(word)) == 0 and word.value == 0
